@@ -1,0 +1,129 @@
+/* C ABI of libmytorch_b200.so — hand-written sm_100a kernels for the CNN training step of
+ * tigert1998/mytorch.
+ *
+ * Conventions
+ *  - Every pointer is a raw device pointer unless a comment says "host".  The caller owns all
+ *    buffers, including scratch ("workspace"); the library allocates nothing and keeps no
+ *    reference after a call returns.
+ *  - 4-D activations and convolution weights are channels-last: x[N][H][W][C],
+ *    w[Cout][KH][KW][Cin].  Everything else is dense row-major.
+ *  - `stream` is a cudaStream_t; work is enqueued on it and the call returns without
+ *    synchronising, so calls may be captured in a CUDA graph.
+ *  - Functions returning int return 0 on success or an MtbStatus code; mtb_last_error() then
+ *    holds a message for the calling thread.  Nothing aborts or traps.
+ *
+ * Each declaration names the reference interface it replaces (file:line inside the
+ * tigert1998/mytorch tree).  The reference's own native entry points return void and take NCHW
+ * tensors; its generated symbol names are <Func>_<dtype> (mytorch/backends/cuda/env.py:201-221).
+ */
+#ifndef MYTORCH_B200_H
+#define MYTORCH_B200_H
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum MtbStatus { MTB_OK = 0, MTB_ERR_INVALID = 1, MTB_ERR_CUDA = 2, MTB_ERR_UNSUPPORTED = 3, MTB_ERR_WORKSPACE = 4, MTB_ERR_DEVICE = 5 };
+
+/* ---- runtime (replaces check_cuda_errors, mytorch/backends/cuda/env.py:26-38) ---- */
+const char* mtb_last_error(void);
+int mtb_version(void);
+int mtb_device_check(void); /* MTB_OK iff the current device is compute capability 10.x */
+
+/* ---- convolution (replaces ConvForwardImplicitGEMM_float32 / ConvBackwardImplicitGEMM_float32,
+ *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from
+ *      mytorch/backends/cuda/ops/conv.py:9-90) ---- */
+long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout);
+/* y[N,OH,OW,Cout] = conv(x[N,H,W,Cin], wt[Cout,KH,KW,Cin]) + bias (bias may be NULL); relu != 0 clamps at 0 */
+int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                           const float* wt, const float* bias, float* y, int relu, void* stream);
+/* dx[N,H,W,Cin]: every element is written (zeros where no window reaches); no atomics */
+int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                         const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream);
+/* dw[Cout,KH,KW,Cin]; split-K partials go to workspace and are summed in a fixed order */
+int mtb_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                         const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream);
+
+/* ---- dense GEMM for Linear / mm (replaces the cublasLtMatmul call site,
+ *      mytorch/backends/cuda/ops/mm.py:10-128, and the permute that materialises W^T,
+ *      mytorch/nn/linear.py:62) ----
+ * C[M,N] = op(A) op(B) (+ bias[N]) (relu). A is [M,K] (trans_a 0) or [K,M]; B is [K,N] (trans_b 0) or [N,K]. */
+int mtb_gemm_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu, float* c,
+                 void* stream);
+
+/* ---- BatchNorm2d (replaces batch_norm2d_reference_<dt> and its backward,
+ *      mytorch/native/cuda/batch_norm.cu/source.cu:134-166 and :269-289) ---- */
+long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w);
+int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps, int training,
+                                 double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var, int relu,
+                                 void* workspace, long long workspace_bytes, void* stream);
+int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
+                                  const float* gamma, double eps, float* dx, float* dgamma, float* dbeta, void* workspace,
+                                  long long workspace_bytes, void* stream);
+
+/* ---- MaxPool2d (replaces max_pool2d_reference / max_pool2d_backward_reference,
+ *      mytorch/native/cuda/pool_ops.cu/1.template:5-52 and 2.template:5-50) ----
+ * tiemask: uint16 per output element, bit kh*KW+kw set where the window element equals the
+ * maximum (padding counts as 0); lowest set bit = argmax. Needs KH*KW <= 16, may be NULL. */
+int mtb_max_pool2d_forward_f32(int n, int c, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, const float* x, float* y,
+                               unsigned short* tiemask, void* stream);
+/* pass tiemask, or out and x (the equality is then recomputed, as the reference does) */
+int mtb_max_pool2d_backward_f32(int n, int c, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, const float* dy,
+                                const unsigned short* tiemask, const float* out, const float* x, float* dx, void* stream);
+int mtb_max_pool2d_argmax_u8(const unsigned short* tiemask, unsigned char* argmax, long long n, void* stream);
+
+/* ---- elementwise (replaces relu_reference / relu_backward_reference / fill_reference,
+ *      mytorch/native/cuda/elementwise_ops.cu/vars.json:2-21, and the same-shape and bias cases of
+ *      add_reference, mytorch/native/cuda/broadcast_binary_ops.cu/1.template) ---- */
+int mtb_fill_f32(float* x, long long n, float value, void* stream);
+int mtb_copy_f32(float* dst, const float* src, long long n, void* stream);
+int mtb_scale_f32(float* dst, const float* src, long long n, float scale, void* stream);
+int mtb_relu_forward_f32(const float* x, float* y, long long n, void* stream);
+int mtb_relu_backward_f32(const float* dy, const float* x, float* dx, long long n, void* stream); /* blocks only x < 0 */
+int mtb_add_f32(const float* x, const float* y, float* z, long long n, float alpha, void* stream); /* z = x + alpha*y */
+int mtb_mul_f32(const float* x, const float* y, float* z, long long n, void* stream);
+int mtb_add_bias_rows_f32(const float* x, const float* bias, float* y, long long rows, int cols, float alpha, void* stream);
+/* general broadcast op over <= 6 logical dims; shape/strides are HOST arrays (strides in elements, 0 broadcasts);
+ * op: 0 add, 1 sub, 2 mul, 3 div, 4 pow, 5 alpha*x (replaces broadcast(), broadcast_utils.cuh:4-37, and
+ * permute_reference, mytorch/native/cuda/basic_ops.cu/source.cu:5-41) */
+int mtb_binary_strided_f32(int op, int ndim, const long long* shape, const long long* x_strides, const long long* y_strides,
+                           const long long* z_strides, const float* x, const float* y, float* z, float alpha, void* stream);
+int mtb_nchw_to_nhwc_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
+int mtb_nhwc_to_nchw_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
+/* kind: 0 int32->int64, 1 int64->float32, 2 float32->int64 (replaces cast_reference, cast.cu/source.cu:5-14) */
+int mtb_cast(int kind, const void* src, void* dst, long long n, void* stream);
+
+/* ---- reductions (replace sum_scale_reference / _backward, mytorch/native/cuda/reduce_ops.cu/1.template, 2.template,
+ *      and ReduceTemplate, reduce_utils.cuh:24-62) ---- */
+long long mtb_colsum_workspace_bytes(int c);
+int mtb_colsum_f32(const float* a, long long rows, int c, float scale, float* out, void* workspace, long long workspace_bytes, void* stream);
+int mtb_nhwc_spatial_sum_f32(const float* x, float* y, int n, int c, int hw, float scale, void* stream);
+int mtb_nhwc_spatial_bcast_f32(const float* dy, float* dx, int n, int c, int hw, float scale, void* stream);
+int mtb_sum_strided_f32(const float* x, float* y, int nkept, const long long* kept_shape, const long long* kept_strides, int nred,
+                        const long long* red_shape, const long long* red_strides, float scale, void* stream);
+
+/* ---- softmax cross-entropy (replaces cross_entropy_reference / _backward_reference,
+ *      mytorch/native/cuda/cross_entropy.cu/source.cu:6-99); target is int64 ---- */
+long long mtb_cross_entropy_workspace_bytes(int batch);
+int mtb_cross_entropy_forward_f32(int batch, int classes, const float* logits, const long long* target, float* loss, void* workspace,
+                                  long long workspace_bytes, void* stream);
+int mtb_cross_entropy_backward_f32(int batch, int classes, const float* logits, const long long* target, const float* dy, float* dlogits,
+                                   void* stream);
+
+/* ---- SGD (replaces sgd_reference, mytorch/native/cuda/optim.cu/source.cu:3-19, launched per parameter from
+ *      mytorch/backends/cuda/ops/sgd.py:8-35) ---- */
+int mtb_sgd_f32(float* param, const float* grad, float* momentum_buffer, long long n, int is_first, double lr, double weight_decay,
+                double momentum, double dampening, int nesterov, int maximize, double grad_scale, void* stream);
+/* params/grads/momentum_buffers/sizes/is_first are HOST arrays of length count */
+int mtb_sgd_multi_f32(int count, float* const* params, const float* const* grads, float* const* momentum_buffers, const long long* sizes,
+                      const int* is_first, double lr, double weight_decay, double momentum, double dampening, int nesterov, int maximize,
+                      double grad_scale, void* stream);
+/* gather gradient tensors into one flat all-reduce buffer (no counterpart: the reference has no
+ * distributed code); srcs/offsets/sizes are HOST arrays */
+int mtb_pack_scale_f32(int count, const float* const* srcs, const long long* offsets, const long long* sizes, float* dst, double scale,
+                       void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,114 @@
+"""Tape-based reverse-mode differentiation.
+
+Observable behaviour follows the reference's ``mytorch/autograd.py``: operators call
+``add_node(name, input_args, output_tensors, helper_tensors)`` (``:33-54``); ``backward``
+(``:120-179``) accepts only a one-element tensor, seeds its gradient with 1, calls each
+operator's registered backward as ``f(*output_grads, *helpers, *input_args)``, zips the returned
+list with ``input_args`` and accumulates into every input that requires a gradient (first
+contribution assigned, later ones added), then forgets the visited graph — a second
+``backward`` through the same graph raises "Make sure you don't backward a tensor twice".
+``no_grad()`` (``:181-196``) is re-entrant.
+
+The implementation differs: every node carries a creation sequence number, so the nodes
+upstream of the loss sorted by descending sequence are already a valid reverse topological
+order — no degree counting, no dictionary keyed by tensors.
+"""
+from __future__ import annotations
+
+
+class _Node:
+    __slots__ = ("name", "inputs", "outputs", "helpers", "seq")
+
+    def __init__(self, name, inputs, outputs, helpers, seq):
+        self.name, self.inputs, self.outputs, self.helpers, self.seq = name, inputs, outputs, helpers, seq
+
+
+class DAGTracker:
+    _instance = None
+
+    @classmethod
+    def instance(cls):
+        if cls._instance is None:
+            cls._instance = cls()
+        return cls._instance
+
+    def __init__(self):
+        self._backward_funcs = {}
+        self._seq = 0
+        self.no_grad = False
+
+    def register_backward_function(self, op_name):
+        def decorator(func):
+            self._backward_funcs[op_name] = func
+            return func
+
+        return decorator
+
+    def add_node(self, name, input_args, output_tensors, helper_tensors=None):
+        self._seq += 1
+        node = _Node(name, list(input_args), list(output_tensors), list(helper_tensors or []), self._seq)
+        for t in output_tensors:
+            t._grad_node = node
+
+    def _upstream(self, root):
+        from mytorch_b200.tensor import Tensor
+
+        seen, stack, nodes = set(), [root], []
+        while stack:
+            node = stack.pop()
+            if id(node) in seen:
+                continue
+            seen.add(id(node))
+            nodes.append(node)
+            for arg in node.inputs:
+                if isinstance(arg, Tensor) and arg._grad_node is not None:
+                    stack.append(arg._grad_node)
+        nodes.sort(key=lambda n: -n.seq)
+        return nodes
+
+    def backward(self, tensor):
+        from mytorch_b200.tensor import MismatchShapesError, Tensor, shape_size
+
+        if tensor._grad_node is None:
+            raise RuntimeError("Make sure you don't backward a tensor twice")
+        if shape_size(tensor.shape) != 1:
+            raise RuntimeError("Backward tensor must be a scalar")
+        order = self._upstream(tensor._grad_node)
+        seed = Tensor(shape=tensor.shape, dtype=tensor.dtype, device=tensor.device)
+        seed.fill_(1)
+        tensor.grad = seed
+
+        for node in order:
+            func = self._backward_funcs[node.name]
+            grads = func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs)
+            for arg, grad in zip(node.inputs, grads):
+                if arg is None or not isinstance(arg, Tensor) or not arg.requires_grad or grad is None:
+                    continue
+                if arg.grad is None:
+                    arg.grad = grad
+                else:
+                    if arg.grad.shape != grad.shape:
+                        raise MismatchShapesError([arg.grad.shape, grad.shape])
+                    arg.grad = arg.grad + grad
+
+        for node in order:
+            for t in node.outputs:
+                t._grad_node = None
+            node.inputs = node.outputs = node.helpers = ()
+
+
+class NoGrad:
+    _depth = 0
+
+    def __enter__(self):
+        NoGrad._depth += 1
+        DAGTracker.instance().no_grad = True
+
+    def __exit__(self, exc_type, exc_value, traceback):
+        NoGrad._depth -= 1
+        if NoGrad._depth == 0:
+            DAGTracker.instance().no_grad = False
+
+
+def no_grad():
+    return NoGrad()

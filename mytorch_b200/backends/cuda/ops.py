@@ -1,0 +1,638 @@
+"""CUDA operator wrappers: allocate outputs, marshal shapes and scalars, call the kernel library.
+
+One function per registry name, with the positional signatures and return containers of the
+reference's ``mytorch/backends/cuda/ops/*.py`` (e.g. ``conv2d`` / ``conv2d_backward``
+``conv.py:9-90``, ``batch_norm2d`` ``batch_norm.py:10-105``, ``max_pool2d`` ``pool_ops.py:95-104``,
+``sgd`` ``sgd.py:8-35``).  No wrapper synchronises, copies metadata to the device or touches the
+host copy of a tensor, so a whole training step can be captured in a CUDA graph.
+
+4-D float32 tensors are channels-last in device memory (see ``tensor.py``); helpers below give
+the logical-dimension strides of either layout to the generic strided kernels.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import numpy as np
+
+from mytorch_b200.backends.backend_dispatcher import BackendDispatcher
+from mytorch_b200.backends.cuda.env import CudaEnv, CudaMemory
+from mytorch_b200.backends.utils import calculate_broadcast_shape, calculate_reduce_shape, calculate_reshaped_shape
+from mytorch_b200.dtype import float32, int32, int64
+
+_reg = BackendDispatcher.instance().register_backend_function
+_LL = ctypes.c_longlong
+
+
+def _T():
+    from mytorch_b200.tensor import Tensor
+
+    return Tensor
+
+
+def _env(t=None):
+    env = CudaEnv.instance()
+    if t is not None:
+        env.set_device(t.device.index)
+    return env
+
+
+def _ptr(t):
+    return None if t is None else t._native_array.ptr
+
+
+def _numel(shape):
+    n = 1
+    for s in shape:
+        n *= s
+    return n
+
+
+def _new(shape, like, dtype=None):
+    return _T()(shape=tuple(shape), dtype=dtype or like.dtype, device=like.device)
+
+
+def _f32(*tensors):
+    from mytorch_b200.tensor import InvalidDataTypeError
+
+    for t in tensors:
+        if t is not None and t.dtype is not float32:
+            raise InvalidDataTypeError(t.dtype)
+
+
+def _nontrivial_nhwc(t):
+    return t._nhwc and t.shape[1] > 1 and t.shape[2] * t.shape[3] > 1
+
+
+def _strides(t):
+    """Element strides of the logical dimensions in device memory."""
+    shape = t.shape
+    if t._nhwc:
+        n, c, h, w = shape
+        return [h * w * c, 1, w * c, c]
+    out, acc = [0] * len(shape), 1
+    for i in range(len(shape) - 1, -1, -1):
+        out[i] = acc
+        acc *= shape[i]
+    return out
+
+
+def _ll(values):
+    return (_LL * max(len(values), 1))(*values)
+
+
+# ---------------------------------------------------------------------------- host <-> device
+
+@_reg("cuda", "upload")
+def cuda_upload(t, array):
+    """Host ndarray (logical layout) -> device storage of ``t`` (channels-last when 4-D float32)."""
+    env = _env(t)
+    array = np.ascontiguousarray(array, dtype=t.dtype.np_dtype)
+    if _nontrivial_nhwc(t):
+        stage = CudaMemory(t.device.index, array.nbytes)
+        stage.write(array)
+        n, c, h, w = t.shape
+        env.lib.nchw_to_nhwc_f32(stage.ptr, _ptr(t), n, c, h, w, env.stream())
+    else:
+        t._native_array.write(array)
+
+
+def upload_into(t, host):
+    """Asynchronously refill an existing device tensor from host memory (NumPy array, or a torch
+    CPU tensor — pinned for a truly asynchronous copy) holding the logical (NCHW) layout.  The
+    staging buffer of a channels-last tensor is allocated once and reused."""
+    env = _env(t)
+    torch = env.torch
+    src = host if isinstance(host, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(host))
+    src = src.reshape(-1).view(torch.uint8)
+    if _nontrivial_nhwc(t):
+        stage = getattr(t, "_stage", None)
+        if stage is None:
+            stage = t._stage = CudaMemory(t.device.index, t._native_array.nbytes)
+        stage.write_from(src)
+        n, c, h, w = t.shape
+        env.lib.nchw_to_nhwc_f32(stage.ptr, _ptr(t), n, c, h, w, env.stream())
+    else:
+        t._native_array.write_from(src)
+
+
+@_reg("cuda", "download")
+def cuda_download(t):
+    env = _env(t)
+    if _nontrivial_nhwc(t):
+        tmp = CudaMemory(t.device.index, t._native_array.nbytes)
+        n, c, h, w = t.shape
+        env.lib.nhwc_to_nchw_f32(_ptr(t), tmp.ptr, n, c, h, w, env.stream())
+        return tmp.read(t.shape, t.dtype.np_dtype)
+    return t._native_array.read(t.shape, t.dtype.np_dtype)
+
+
+# ---------------------------------------------------------------------------- convolution
+
+def _conv_args(x, w, stride, padding):
+    n, cin, h, wd = x.shape
+    cout, cin2, kh, kw = w.shape
+    if cin != cin2:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([x.shape, w.shape])
+    return (n, cin, h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1], cout)
+
+
+@_reg("cuda", "conv2d")
+def cuda_conv2d(input, weight, bias, stride, padding):
+    _f32(input, weight, bias)
+    env = _env(input)
+    a = _conv_args(input, weight, stride, padding)
+    n, cin, h, w, kh, kw, sh, sw, ph, pw, cout = a
+    oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
+    out = _new((n, cout, oh, ow), input)
+    env.lib.conv2d_forward_f32(*a, _ptr(input), _ptr(weight), _ptr(bias), _ptr(out), 0, env.stream())
+    return out
+
+
+@_reg("cuda", "conv2d_backward")
+def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding):
+    _f32(output_grad, input, weight)
+    env = _env(input)
+    a = _conv_args(input, weight, stride, padding)
+    st = env.stream()
+    ws, ws_bytes = env.workspace(env.lib.conv2d_workspace_bytes(*a))
+    dx = dw = db = None
+    if input.requires_grad:
+        dx = _new(input.shape, input)
+        env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(dx), ws, ws_bytes, st)
+    if weight.requires_grad:
+        dw = _new(weight.shape, weight)
+        env.lib.conv2d_wgrad_f32(*a, _ptr(input), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)
+    if bias is not None and bias.requires_grad:
+        db = _colsum(env, output_grad, _numel(output_grad.shape) // a[-1], a[-1], bias)
+    return [dx, dw, db]
+
+
+def _colsum(env, mat, rows, cols, like, scale=1.0):
+    out = _new((cols,), like)
+    ws, ws_bytes = env.workspace(env.lib.colsum_workspace_bytes(cols))
+    env.lib.colsum_f32(_ptr(mat), rows, cols, scale, _ptr(out), ws, ws_bytes, env.stream())
+    return out
+
+
+# ---------------------------------------------------------------------------- linear / mm
+
+def _gemm(env, m, n, k, a, ta, b, tb, bias, relu, c):
+    env.lib.gemm_f32(m, n, k, _ptr(a), ta, _ptr(b), tb, _ptr(bias), relu, _ptr(c), env.stream())
+
+
+@_reg("cuda", "linear")
+def cuda_linear(x, weight, bias):
+    _f32(x, weight, bias)
+    env = _env(x)
+    b, fin = x.shape
+    fout = weight.shape[0]
+    if weight.shape[1] != fin:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([x.shape, weight.shape])
+    y = _new((b, fout), x)
+    _gemm(env, b, fout, fin, x, 0, weight, 1, bias, 0, y)
+    return y
+
+
+@_reg("cuda", "linear_backward")
+def cuda_linear_backward(output_grad, x, weight, bias):
+    env = _env(x)
+    b, fin = x.shape
+    fout = weight.shape[0]
+    dx = dw = db = None
+    if x.requires_grad:
+        dx = _new(x.shape, x)
+        _gemm(env, b, fin, fout, output_grad, 0, weight, 0, None, 0, dx)
+    if weight.requires_grad:
+        dw = _new(weight.shape, weight)
+        _gemm(env, fout, fin, b, output_grad, 1, x, 0, None, 0, dw)
+    if bias is not None and bias.requires_grad:
+        db = _colsum(env, output_grad, b, fout, bias)
+    return [dx, dw, db]
+
+
+@_reg("cuda", "mm")
+def cuda_mm(x, y):
+    _f32(x, y)
+    env = _env(x)
+    (m, k), (k2, n) = x.shape, y.shape
+    if k != k2:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([x.shape, y.shape])
+    z = _new((m, n), x)
+    _gemm(env, m, n, k, x, 0, y, 0, None, 0, z)
+    return z
+
+
+@_reg("cuda", "mm_backward")
+def cuda_mm_backward(output_grad, x, y):
+    env = _env(x)
+    (m, k), n = x.shape, y.shape[1]
+    dx, dy = _new(x.shape, x), _new(y.shape, y)
+    _gemm(env, m, k, n, output_grad, 0, y, 1, None, 0, dx)
+    _gemm(env, k, n, m, x, 1, output_grad, 0, None, 0, dy)
+    return dx, dy
+
+
+# ---------------------------------------------------------------------------- batch norm
+
+@_reg("cuda", "batch_norm2d")
+def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, running_var):
+    _f32(x, weight, bias, running_mean, running_var)
+    env = _env(x)
+    n, c, h, w = x.shape
+    y, mean, var = _new(x.shape, x), _new((c,), x), _new((c,), x)
+    ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
+    env.lib.batch_norm2d_forward_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), int(bool(training)), float(momentum),
+                                     _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), 0, ws, ws_bytes, env.stream())
+    return y, mean, var
+
+
+@_reg("cuda", "batch_norm2d_backward")
+def cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps):
+    env = _env(x)
+    n, c, h, w = x.shape
+    dx = _new(x.shape, x)
+    affine = weight is not None and bias is not None
+    dg = _new((c,), x) if affine else None
+    db = _new((c,), x) if affine else None
+    ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
+    env.lib.batch_norm2d_backward_f32(n, c, h, w, _ptr(output_grad), _ptr(mean), _ptr(var), _ptr(x), _ptr(weight), float(eps),
+                                      _ptr(dx), _ptr(dg), _ptr(db), ws, ws_bytes, env.stream())
+    return [dx, dg, db]
+
+
+# ---------------------------------------------------------------------------- pooling
+
+def _pool_args(x, kernel_size, stride, padding):
+    pair = lambda v: (v, v) if isinstance(v, int) else tuple(v)
+    kh, kw = pair(kernel_size)
+    sh, sw = pair(kernel_size if stride is None else stride)
+    ph, pw = pair(padding)
+    n, c, h, w = x.shape
+    return (n, c, h, w, kh, kw, sh, sw, ph, pw)
+
+
+@_reg("cuda", "max_pool2d")
+def cuda_max_pool2d(x, kernel_size, stride, padding):
+    _f32(x)
+    env = _env(x)
+    a = _pool_args(x, kernel_size, stride, padding)
+    n, c, h, w, kh, kw, sh, sw, ph, pw = a
+    oh, ow = (2 * ph + h - kh) // sh + 1, (2 * pw + w - kw) // sw + 1
+    y = _new((n, c, oh, ow), x)
+    mask = CudaMemory(x.device.index, 2 * _numel(y.shape)) if kh * kw <= 16 else None
+    env.lib.max_pool2d_forward_f32(*a, _ptr(x), _ptr(y), mask.ptr if mask else None, env.stream())
+    y._pool_tiemask = mask  # uint16 per output element, channels-last like y
+    return y
+
+
+@_reg("cuda", "max_pool2d_backward")
+def cuda_max_pool2d_backward(output_grad, output, x, kernel_size, stride, padding):
+    env = _env(x)
+    a = _pool_args(x, kernel_size, stride, padding)
+    dx = _new(x.shape, x)
+    mask = getattr(output, "_pool_tiemask", None)
+    env.lib.max_pool2d_backward_f32(*a, _ptr(output_grad), mask.ptr if mask else None, _ptr(output), _ptr(x), _ptr(dx), env.stream())
+    return [dx]
+
+
+def max_pool2d_argmax(output):
+    """Window-local index (kh*KW + kw) of the first maximum for every output element, as a host
+    uint8 array in logical [N,C,OH,OW] order.  Derived from the tie mask written by forward."""
+    env = _env(output)
+    mask = getattr(output, "_pool_tiemask", None)
+    if mask is None:
+        raise RuntimeError("this tensor was not produced by max_pool2d with a window of at most 16 elements")
+    n, c, oh, ow = output.shape
+    total = n * c * oh * ow
+    arg = CudaMemory(output.device.index, total)
+    env.lib.max_pool2d_argmax_u8(mask.ptr, arg.ptr, total, env.stream())
+    return arg.read((n, oh, ow, c), np.uint8).transpose(0, 3, 1, 2).copy()
+
+
+# ---------------------------------------------------------------------------- elementwise
+
+@_reg("cuda", "relu")
+def cuda_relu(x):
+    _f32(x)
+    env = _env(x)
+    y = _new(x.shape, x)
+    env.lib.relu_forward_f32(_ptr(x), _ptr(y), _numel(x.shape), env.stream())
+    return y
+
+
+@_reg("cuda", "relu_backward")
+def cuda_relu_backward(output_grad, x):
+    env = _env(x)
+    dx = _new(x.shape, x)
+    env.lib.relu_backward_f32(_ptr(output_grad), _ptr(x), _ptr(dx), _numel(x.shape), env.stream())
+    return [dx]
+
+
+@_reg("cuda", "fill")
+def cuda_fill(x, value):
+    env = _env(x)
+    if x.dtype is float32:
+        env.lib.fill_f32(_ptr(x), _numel(x.shape), float(value), env.stream())
+    else:
+        x._native_array.write(np.full(x.shape, value, dtype=x.dtype.np_dtype))
+
+
+def _host_random(x, array):
+    cuda_upload(x, array.astype(x.dtype.np_dtype))
+
+
+@_reg("cuda", "uniform")
+def cuda_uniform(x, seed, a, b):
+    # Initialisation only: drawn on the host with the reference CPU recipe, then uploaded, so a
+    # model initialised on the GPU has the same weights as one initialised on the CPU.
+    np.random.seed(seed)
+    _host_random(x, np.random.uniform(low=a, high=b, size=x.shape))
+
+
+@_reg("cuda", "normal")
+def cuda_normal(x, seed, mean, stddev):
+    np.random.seed(seed)
+    _host_random(x, np.random.normal(mean, stddev, x.shape))
+
+
+@_reg("cuda", "copy")
+def cuda_copy(dst, src):
+    env = _env(dst)
+    if dst.shape != src.shape:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([dst.shape, src.shape])
+    if dst.dtype is float32:
+        env.lib.copy_f32(_ptr(dst), _ptr(src), _numel(dst.shape), env.stream())
+    else:
+        nbytes = dst._native_array.nbytes
+        dst._native_array._buf[:nbytes].copy_(src._native_array._buf[:nbytes])
+
+
+@_reg("cuda", "cast")
+def cuda_cast(x, dtype):
+    env = _env(x)
+    kinds = {(int32, int64): 0, (int64, float32): 1, (float32, int64): 2}
+    kind = kinds.get((x.dtype, dtype))
+    if kind is None:
+        raise RuntimeError(f"cast from {x.dtype} to {dtype} is not available on the cuda backend")
+    if x._nhwc or (len(x.shape) == 4 and dtype is float32):
+        raise RuntimeError("cast of 4-D tensors between float32 and integer types is not available on the cuda backend")
+    out = _new(x.shape, x, dtype)
+    env.lib.cast(kind, _ptr(x), _ptr(out), _numel(x.shape), env.stream())
+    return out
+
+
+# ---------------------------------------------------------------------------- broadcast binary ops
+
+_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4}
+
+
+def _bstrides(t, out_shape):
+    """Strides of ``t`` along the dimensions of ``out_shape`` (0 where ``t`` broadcasts)."""
+    pad = len(out_shape) - len(t.shape)
+    st = _strides(t)
+    return [0] * pad + [0 if t.shape[i] == 1 and out_shape[pad + i] != 1 else st[i] for i in range(len(t.shape))]
+
+
+def _binary(name, x, y, alpha=1.0):
+    _f32(x, y)
+    env = _env(x)
+    shape = calculate_broadcast_shape(x.shape, y.shape)
+    z = _new(shape, x)
+    n = _numel(shape)
+    if x.shape == y.shape and name in ("add", "sub", "mul"):
+        if name == "mul":
+            env.lib.mul_f32(_ptr(x), _ptr(y), _ptr(z), n, env.stream())
+        else:
+            env.lib.add_f32(_ptr(x), _ptr(y), _ptr(z), n, float(alpha) if name == "add" else -float(alpha), env.stream())
+        return z
+    if name == "add" and len(x.shape) == 2 and y.shape == (x.shape[1],):
+        env.lib.add_bias_rows_f32(_ptr(x), _ptr(y), _ptr(z), x.shape[0], x.shape[1], float(alpha), env.stream())
+        return z
+    env.lib.binary_strided_f32(_OPS[name], len(shape), _ll(shape), _ll(_bstrides(x, shape)), _ll(_bstrides(y, shape)),
+                               _ll(_strides(z)), _ptr(x), _ptr(y), _ptr(z), float(alpha), env.stream())
+    return z
+
+
+def _scaled(t, scale):
+    if scale == 1:
+        return t
+    env = _env(t)
+    out = _new(t.shape, t)
+    env.lib.scale_f32(_ptr(out), _ptr(t), _numel(t.shape), float(scale), env.stream())
+    return out
+
+
+def _reduce_to(g, shape, like):
+    """Sum ``g`` over the dimensions along which a tensor of ``shape`` was broadcast."""
+    if tuple(g.shape) == tuple(shape):
+        return g
+    pad = len(g.shape) - len(shape)
+    dims = tuple(i for i in range(len(g.shape)) if i < pad or (shape[i - pad] == 1 and g.shape[i] != 1))
+    out = cuda_sum_scale(g, dims, True, 1)
+    return cuda_reshape(out, shape)
+
+
+@_reg("cuda", "add")
+def cuda_add(x, y, alpha):
+    return _binary("add", x, y, alpha)
+
+
+@_reg("cuda", "sub")
+def cuda_sub(x, y, alpha):
+    return _binary("sub", x, y, alpha)
+
+
+@_reg("cuda", "mul")
+def cuda_mul(x, y):
+    return _binary("mul", x, y)
+
+
+@_reg("cuda", "div")
+def cuda_div(x, y):
+    return _binary("div", x, y)
+
+
+@_reg("cuda", "pow")
+def cuda_pow(x, y):
+    return _binary("pow", x, y)
+
+
+@_reg("cuda", "add_backward")
+def cuda_add_backward(output_grad, x, y, alpha):
+    # Same-shape operands receive the upstream gradient itself (no copy): nothing mutates
+    # gradients in place, accumulation always writes a fresh tensor.
+    return _reduce_to(output_grad, x.shape, x), _reduce_to(_scaled(output_grad, alpha), y.shape, y)
+
+
+@_reg("cuda", "sub_backward")
+def cuda_sub_backward(output_grad, x, y, alpha):
+    return _reduce_to(output_grad, x.shape, x), _reduce_to(_scaled(output_grad, -alpha), y.shape, y)
+
+
+@_reg("cuda", "mul_backward")
+def cuda_mul_backward(output_grad, x, y):
+    return _reduce_to(_binary("mul", output_grad, y), x.shape, x), _reduce_to(_binary("mul", output_grad, x), y.shape, y)
+
+
+# ---------------------------------------------------------------------------- reductions
+
+@_reg("cuda", "sum_scale")
+def cuda_sum_scale(x, dim, keepdim, scale):
+    _f32(x)
+    env = _env(x)
+    dim = tuple(dim)
+    out_shape = calculate_reduce_shape(x.shape, dim, keepdim)
+    out = _new(out_shape, x)
+    st = env.stream()
+    if x._nhwc and dim == (2, 3):
+        n, c, h, w = x.shape
+        env.lib.nhwc_spatial_sum_f32(_ptr(x), _ptr(out), n, c, h * w, float(scale), st)
+        return out
+    if x._nhwc and dim == (0, 2, 3):
+        n, c, h, w = x.shape
+        ws, ws_bytes = env.workspace(env.lib.colsum_workspace_bytes(c))
+        env.lib.colsum_f32(_ptr(x), n * h * w, c, float(scale), _ptr(out), ws, ws_bytes, st)
+        return out
+    xs = _strides(x)
+    kept = [i for i in range(len(x.shape)) if i not in dim]
+    red = list(dim)
+    dense = out if not _nontrivial_nhwc(out) else _T()(shape=(_numel(out_shape),), dtype=x.dtype, device=x.device)
+    env.lib.sum_strided_f32(_ptr(x), _ptr(dense), len(kept), _ll([x.shape[i] for i in kept]), _ll([xs[i] for i in kept]),
+                            len(red), _ll([x.shape[i] for i in red]), _ll([xs[i] for i in red]), float(scale), st)
+    if dense is not out:
+        n, c, h, w = out_shape
+        env.lib.nchw_to_nhwc_f32(_ptr(dense), _ptr(out), n, c, h, w, st)
+    return out
+
+
+@_reg("cuda", "sum_scale_backward")
+def cuda_sum_scale_backward(output_grad, x, dim, keepdim, scale):
+    env = _env(x)
+    dim = tuple(dim)
+    dx = _new(x.shape, x)
+    st = env.stream()
+    if x._nhwc and dim == (2, 3):
+        n, c, h, w = x.shape
+        env.lib.nhwc_spatial_bcast_f32(_ptr(output_grad), _ptr(dx), n, c, h * w, float(scale), st)
+        return [dx]
+    gs = _strides(output_grad)
+    if keepdim:
+        src = [0 if i in dim else gs[i] for i in range(len(x.shape))]
+    else:
+        it = iter(gs)
+        src = [0 if i in dim else next(it) for i in range(len(x.shape))]
+    env.lib.binary_strided_f32(5, len(x.shape), _ll(x.shape), _ll(src), _ll(src), _ll(_strides(dx)), _ptr(output_grad), None,
+                               _ptr(dx), float(scale), st)
+    return [dx]
+
+
+# ---------------------------------------------------------------------------- shape ops
+
+def _dense_copy(env, t):
+    """Logical row-major copy of a channels-last tensor."""
+    n, c, h, w = t.shape
+    out = CudaMemory(t.device.index, t._native_array.nbytes)
+    env.lib.nhwc_to_nchw_f32(_ptr(t), out.ptr, n, c, h, w, env.stream())
+    return out
+
+
+@_reg("cuda", "reshape")
+def cuda_reshape(x, shape):
+    from mytorch_b200.tensor import channels_last
+
+    env = _env(x)
+    new_shape = calculate_reshaped_shape(x.shape, shape)
+    out = _T()(tensor=x)
+    out.shape = tuple(new_shape)
+    out._nhwc = channels_last(out.shape, out.dtype, "cuda")
+    mem = x._native_array
+    if _nontrivial_nhwc(x):
+        mem = _dense_copy(env, x)
+    if _nontrivial_nhwc(out):
+        n, c, h, w = out.shape
+        dst = CudaMemory(x.device.index, mem.nbytes)
+        env.lib.nchw_to_nhwc_f32(mem.ptr, dst.ptr, n, c, h, w, env.stream())
+        mem = dst
+    out._native_array = mem
+    return out
+
+
+@_reg("cuda", "permute")
+def cuda_permute(x, dims):
+    _f32(x)
+    env = _env(x)
+    out = _new([x.shape[d] for d in dims], x)
+    xs = _strides(x)
+    src = [xs[d] for d in dims]
+    env.lib.binary_strided_f32(5, len(dims), _ll(out.shape), _ll(src), _ll(src), _ll(_strides(out)), _ptr(x), None, _ptr(out), 1.0,
+                               env.stream())
+    return out
+
+
+@_reg("cuda", "permute_backward")
+def cuda_permute_backward(output_grad, x, dims):
+    inverse = [0] * len(dims)
+    for i, d in enumerate(dims):
+        inverse[d] = i
+    return [cuda_permute(output_grad, tuple(inverse))]
+
+
+# ---------------------------------------------------------------------------- loss
+
+@_reg("cuda", "cross_entropy")
+def cuda_cross_entropy(input, target):
+    from mytorch_b200.tensor import InvalidDataTypeError
+
+    if target.dtype is not int64:
+        raise InvalidDataTypeError(target.dtype)
+    _f32(input)
+    env = _env(input)
+    b, c = input.shape
+    loss = _new((1,), input)
+    ws, ws_bytes = env.workspace(env.lib.cross_entropy_workspace_bytes(b))
+    env.lib.cross_entropy_forward_f32(b, c, _ptr(input), _ptr(target), _ptr(loss), ws, ws_bytes, env.stream())
+    return loss
+
+
+@_reg("cuda", "cross_entropy_backward")
+def cuda_cross_entropy_backward(output_grad, input, target):
+    env = _env(input)
+    b, c = input.shape
+    dx = _new(input.shape, input)
+    env.lib.cross_entropy_backward_f32(b, c, _ptr(input), _ptr(target), _ptr(output_grad), _ptr(dx), env.stream())
+    return [dx]
+
+
+# ---------------------------------------------------------------------------- optimiser
+
+@_reg("cuda", "sgd")
+def cuda_sgd(param, momentum_buffer, is_first_time, lr, weight_decay, momentum, dampening, nesterov, maximize):
+    env = _env(param)
+    env.lib.sgd_f32(_ptr(param), _ptr(param.grad), _ptr(momentum_buffer), _numel(param.shape), int(bool(is_first_time)), float(lr),
+                    float(weight_decay), float(momentum), float(dampening), int(bool(nesterov)), int(bool(maximize)), 1.0, env.stream())
+
+
+@_reg("cuda", "sgd_multi")
+def cuda_sgd_multi(entries, lr, weight_decay, momentum, dampening, nesterov, maximize, grad_scale=1.0):
+    """entries: [(param, momentum_buffer, is_first_time)]; one launch per 96 tensors."""
+    if not entries:
+        return
+    env = _env(entries[0][0])
+    k = len(entries)
+    vp = ctypes.c_void_p
+    params = (vp * k)(*[_ptr(p) for p, _, _ in entries])
+    grads = (vp * k)(*[_ptr(p.grad) for p, _, _ in entries])
+    bufs = (vp * k)(*[_ptr(b) for _, b, _ in entries])
+    sizes = (_LL * k)(*[_numel(p.shape) for p, _, _ in entries])
+    first = (ctypes.c_int * k)(*[int(bool(f)) for _, _, f in entries])
+    env.lib.sgd_multi_f32(k, params, grads, bufs, sizes, first, float(lr), float(weight_decay), float(momentum), float(dampening),
+                          int(bool(nesterov)), int(bool(maximize)), float(grad_scale), env.stream())

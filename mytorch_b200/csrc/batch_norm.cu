@@ -1,0 +1,353 @@
+// BatchNorm2d forward / backward over channels-last activations viewed as a [rows = N*H*W, C]
+// matrix.  HBM-bound: forward reads x twice and writes y once (3S), backward reads x and dy
+// twice and writes dx once (5S).  Per-channel statistics come from per-CTA Welford-style
+// partials (shifted sums, Chan merge) combined in a fixed order by a one-CTA-per-256-channels
+// finalise kernel, so results are bit-reproducible.
+#include "colreduce.cuh"
+
+namespace {
+
+// ---------------------------------------------------------------- forward: statistics
+
+template <int V>
+__global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __restrict__ x, long long rows, int C, int L, long long rows_per_block,
+                                                                float* __restrict__ partial) {
+  const int lane = threadIdx.x & (L - 1);
+  const int rsub = threadIdx.x / L;
+  const int R = 256 / L;
+  const int cg = blockIdx.x * L + lane;  // column group
+  const bool active = cg * V < C;
+  long long r0 = blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+
+  float pivot[V], s1[V], s2[V];
+  int cnt = 0;
+#pragma unroll
+  for (int i = 0; i < V; ++i) { pivot[i] = 0.f; s1[i] = 0.f; s2[i] = 0.f; }
+  if (active) {
+    long long r = r0 + rsub;
+    if (r < r1) {
+      VecF<V> f = vload<V>(x + r * C + (long long)cg * V);
+#pragma unroll
+      for (int i = 0; i < V; ++i) pivot[i] = f.v[i];
+      cnt = 1;
+      r += R;
+    }
+#pragma unroll 4
+    for (; r < r1; r += R) {
+      VecF<V> f = vload<V>(x + r * C + (long long)cg * V);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float d = f.v[i] - pivot[i];
+        s1[i] += d;
+        s2[i] += d * d;
+      }
+      ++cnt;
+    }
+  }
+  __shared__ float sm_mean[V][256];
+  __shared__ float sm_m2[V][256];
+  __shared__ int sm_cnt[256];
+  float inv = cnt > 0 ? 1.f / (float)cnt : 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    sm_mean[i][threadIdx.x] = pivot[i] + s1[i] * inv;
+    sm_m2[i][threadIdx.x] = s2[i] - s1[i] * s1[i] * inv;
+  }
+  sm_cnt[threadIdx.x] = cnt;
+  __syncthreads();
+  if (rsub == 0 && active) {
+    float n = (float)cnt;
+    float mean[V], m2[V];
+#pragma unroll
+    for (int i = 0; i < V; ++i) { mean[i] = sm_mean[i][lane]; m2[i] = sm_m2[i][lane]; }
+    for (int k = 1; k < R; ++k) {
+      float nb = (float)sm_cnt[k * L + lane];
+      if (nb == 0.f) continue;
+      float nt = n + nb;
+      float wb = nb / nt;
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        float d = sm_mean[i][k * L + lane] - mean[i];
+        mean[i] += d * wb;
+        m2[i] += sm_m2[i][k * L + lane] + d * d * n * wb;
+      }
+      n = nt;
+    }
+    float* p = partial + (long long)blockIdx.y * 3 * C + (long long)cg * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      p[i] = n;
+      p[C + i] = mean[i];
+      p[2 * C + i] = m2[i];
+    }
+  }
+}
+
+// One thread per channel merges the P partials in order (double precision, tiny), writes the
+// batch mean / biased variance, the per-channel scale gamma/sqrt(var+eps) used by the
+// normalise pass, and blends the running statistics.
+__global__ void bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
+                                      float one_minus_m, float m, float* running_mean, float* running_var,
+                                      float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double n = 0, mean = 0, m2 = 0;
+  for (int p = 0; p < P; ++p) {
+    double nb = partial[(long long)p * 3 * C + c];
+    if (nb == 0) continue;
+    double mb = partial[(long long)p * 3 * C + C + c];
+    double qb = partial[(long long)p * 3 * C + 2 * C + c];
+    double nt = n + nb;
+    double d = mb - mean;
+    mean += d * nb / nt;
+    m2 += qb + d * d * n * nb / nt;
+    n = nt;
+  }
+  float mu = (float)mean;
+  float var = n > 0 ? (float)(m2 / n) : 0.f;
+  mean_out[c] = mu;
+  var_out[c] = var;
+  float rstd = 1.0f / sqrtf(var + eps);
+  scale_out[c] = gamma ? gamma[c] * rstd : rstd;
+  if (running_mean) running_mean[c] = __fadd_rn(__fmul_rn(one_minus_m, running_mean[c]), __fmul_rn(m, mu));
+  if (running_var) running_var[c] = __fadd_rn(__fmul_rn(one_minus_m, running_var[c]), __fmul_rn(m, var));
+}
+
+// Inference mode: statistics are the running ones.
+__global__ void bn_eval_prep_kernel(int C, const float* __restrict__ gamma, float eps, const float* __restrict__ rm, const float* __restrict__ rv,
+                                    float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  mean_out[c] = rm[c];
+  var_out[c] = rv[c];
+  float rstd = 1.0f / sqrtf(rv[c] + eps);
+  scale_out[c] = gamma ? gamma[c] * rstd : rstd;
+}
+
+// ---------------------------------------------------------------- forward: normalise
+
+template <int V, bool RELU>
+__global__ void __launch_bounds__(256) bn_normalize_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int C, int L,
+                                                            long long rows_per_block, const float* __restrict__ mean,
+                                                            const float* __restrict__ scale, const float* __restrict__ beta) {
+  const int lane = threadIdx.x & (L - 1);
+  const int rsub = threadIdx.x / L;
+  const int R = 256 / L;
+  const int cg = blockIdx.x * L + lane;
+  if (cg * V >= C) return;
+  float mu[V], g[V], b[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    mu[i] = mean[cg * V + i];
+    g[i] = scale[cg * V + i];
+    b[i] = beta ? beta[cg * V + i] : 0.f;
+  }
+  long long r0 = blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+#pragma unroll 4
+  for (long long r = r0 + rsub; r < r1; r += R) {
+    long long off = r * C + (long long)cg * V;
+    VecF<V> f = vload<V>(x + off);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      float t = (f.v[i] - mu[i]) * g[i] + b[i];
+      f.v[i] = RELU ? fmaxf(t, 0.f) : t;
+    }
+    vstore<V>(y + off, f);
+  }
+}
+
+// ---------------------------------------------------------------- backward
+
+// partial[p][0][c] = sum dy, partial[p][1][c] = sum dy * xhat over the CTA's rows.
+template <int V>
+__global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __restrict__ dy, const float* __restrict__ x, long long rows, int C, int L,
+                                                              long long rows_per_block, const float* __restrict__ mean,
+                                                              const float* __restrict__ var, float eps, float* __restrict__ partial) {
+  const int lane = threadIdx.x & (L - 1);
+  const int rsub = threadIdx.x / L;
+  const int R = 256 / L;
+  const int cg = blockIdx.x * L + lane;
+  const bool active = cg * V < C;
+  float mu[V], rstd[V], a0[V], a1[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    a0[i] = 0.f; a1[i] = 0.f;
+    mu[i] = active ? mean[cg * V + i] : 0.f;
+    rstd[i] = active ? 1.0f / sqrtf(var[cg * V + i] + eps) : 0.f;
+  }
+  long long r0 = blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+  if (active) {
+#pragma unroll 4
+    for (long long r = r0 + rsub; r < r1; r += R) {
+      long long off = r * C + (long long)cg * V;
+      VecF<V> g = vload<V>(dy + off);
+      VecF<V> f = vload<V>(x + off);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        a0[i] += g.v[i];
+        a1[i] += g.v[i] * ((f.v[i] - mu[i]) * rstd[i]);
+      }
+    }
+  }
+  __shared__ float sm0[V][256];
+  __shared__ float sm1[V][256];
+#pragma unroll
+  for (int i = 0; i < V; ++i) { sm0[i][threadIdx.x] = a0[i]; sm1[i][threadIdx.x] = a1[i]; }
+  __syncthreads();
+  if (rsub == 0 && active) {
+    for (int k = 1; k < R; ++k) {
+#pragma unroll
+      for (int i = 0; i < V; ++i) { a0[i] += sm0[i][k * L + lane]; a1[i] += sm1[i][k * L + lane]; }
+    }
+    float* p = partial + (long long)blockIdx.y * 2 * C + (long long)cg * V;
+#pragma unroll
+    for (int i = 0; i < V; ++i) { p[i] = a0[i]; p[C + i] = a1[i]; }
+  }
+}
+
+// dbeta = sum dy, dgamma = sum dy*xhat; coefficients for dx = k1 * (dy - k2 - (x - mean) * k3).
+__global__ void bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
+                                    const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
+                                    float* __restrict__ dbeta, float* __restrict__ coef) {
+  int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  double s0 = 0, s1 = 0;
+  for (int p = 0; p < P; ++p) {
+    s0 += partial[(long long)p * 2 * C + c];
+    s1 += partial[(long long)p * 2 * C + C + c];
+  }
+  float db = (float)s0, dg = (float)s1;
+  if (dbeta) dbeta[c] = db;
+  if (dgamma) dgamma[c] = dg;
+  float rstd = 1.0f / sqrtf(var[c] + eps);
+  float gm = gamma ? gamma[c] : 1.f;
+  coef[c] = gm * rstd;               // k1
+  coef[C + c] = db * inv_m;          // k2
+  coef[2 * C + c] = rstd * dg * inv_m;  // k3: (x - mean) * k3 = xhat * dgamma / m
+}
+
+template <int V>
+__global__ void __launch_bounds__(256) bn_bwd_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x, float* __restrict__ dx,
+                                                         long long rows, int C, int L, long long rows_per_block,
+                                                         const float* __restrict__ mean, const float* __restrict__ coef) {
+  const int lane = threadIdx.x & (L - 1);
+  const int rsub = threadIdx.x / L;
+  const int R = 256 / L;
+  const int cg = blockIdx.x * L + lane;
+  if (cg * V >= C) return;
+  float mu[V], k1[V], k2[V], k3[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) {
+    mu[i] = mean[cg * V + i];
+    k1[i] = coef[cg * V + i];
+    k2[i] = coef[C + cg * V + i];
+    k3[i] = coef[2 * C + cg * V + i];
+  }
+  long long r0 = blockIdx.y * rows_per_block;
+  long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
+#pragma unroll 4
+  for (long long r = r0 + rsub; r < r1; r += R) {
+    long long off = r * C + (long long)cg * V;
+    VecF<V> g = vload<V>(dy + off);
+    VecF<V> f = vload<V>(x + off);
+#pragma unroll
+    for (int i = 0; i < V; ++i) g.v[i] = k1[i] * (g.v[i] - k2[i] - (f.v[i] - mu[i]) * k3[i]);
+    vstore<V>(dx + off, g);
+  }
+}
+
+// A streaming pass wants more CTAs than a reduction (no partial rows to combine afterwards).
+ColCfg stream_cfg(long long rows, int C, bool aligned) {
+  ColCfg c = mtb_col_cfg(rows, C, aligned);
+  long long target = (long long)mtb_sm_count() * 8 / c.col_blocks;
+  if (target < 1) target = 1;
+  long long min_rows = (long long)c.rows_per_iter * 4;
+  long long want = (rows + min_rows - 1) / min_rows;
+  if (want < 1) want = 1;
+  long long rb = want < target ? want : target;
+  long long rpb = (rows + rb - 1) / rb;
+  rpb = (rpb + c.rows_per_iter - 1) / c.rows_per_iter * c.rows_per_iter;
+  c.rows_per_block = rpb;
+  c.row_blocks = (int)((rows + rpb - 1) / rpb);
+  return c;
+}
+
+}  // namespace
+
+// Scratch the forward and backward entry points need, in bytes (an upper bound for the shape).
+MTB_API long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w) {
+  (void)n; (void)h; (void)w;
+  long long floats = (long long)mtb_col_max_partials() * 3 * c + 4LL * c;
+  return floats * 4 + 256;
+}
+
+// Training: batch statistics (biased variance also goes into running_var). Inference: running
+// statistics. x, y are channels-last [N,H,W,C]; mean/var outputs are [C]. gamma/beta/running_*
+// may be NULL. relu != 0 applies max(0, .) to y in the same pass.
+MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps,
+                                         int training, double momentum, float* running_mean, float* running_var, float* y,
+                                         float* mean, float* var, int relu, void* workspace, long long workspace_bytes, void* stream) {
+  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && x && y && mean && var && workspace, "batch_norm2d_forward: bad arguments");
+  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_forward: workspace too small");
+  MTB_REQUIRE(training || (running_mean && running_var), "batch_norm2d_forward: inference needs running statistics");
+  cudaStream_t st = (cudaStream_t)stream;
+  long long rows = (long long)n * h * w;
+  bool aligned = mtb_aligned16(x) && mtb_aligned16(y);
+  float* partial = (float*)workspace;
+  float* scale = partial + (long long)mtb_col_max_partials() * 3 * c;
+  int fin_blocks = mtb_div_up(c, 128);
+  if (training) {
+    ColCfg cfg = mtb_col_cfg(rows, c, aligned);
+    dim3 grid(cfg.col_blocks, cfg.row_blocks);
+    if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+    else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+    MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
+    bn_stats_final_kernel<<<fin_blocks, 128, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+                                                      running_mean, running_var, mean, var, scale);
+    MTB_LAUNCH_CHECK("bn_stats_final_kernel");
+  } else {
+    bn_eval_prep_kernel<<<fin_blocks, 128, 0, st>>>(c, gamma, (float)eps, running_mean, running_var, mean, var, scale);
+    MTB_LAUNCH_CHECK("bn_eval_prep_kernel");
+  }
+  ColCfg s = stream_cfg(rows, c, aligned);
+  dim3 grid(s.col_blocks, s.row_blocks);
+  if (s.vec == 4) {
+    if (relu) bn_normalize_kernel<4, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+    else bn_normalize_kernel<4, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+  } else {
+    if (relu) bn_normalize_kernel<1, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+    else bn_normalize_kernel<1, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+  }
+  MTB_LAUNCH_CHECK("bn_normalize_kernel");
+  return MTB_OK;
+}
+
+// dx = gamma/sigma * (dy - dbeta/m - xhat * dgamma/m); dgamma, dbeta may be NULL (not affine).
+MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
+                                          const float* gamma, double eps, float* dx, float* dgamma, float* dbeta, void* workspace,
+                                          long long workspace_bytes, void* stream) {
+  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && dy && mean && var && x && dx && workspace, "batch_norm2d_backward: bad arguments");
+  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_backward: workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  long long rows = (long long)n * h * w;
+  bool aligned = mtb_aligned16(x) && mtb_aligned16(dy) && mtb_aligned16(dx);
+  float* partial = (float*)workspace;
+  float* coef = partial + (long long)mtb_col_max_partials() * 3 * c;  // 3*C floats fit in the 4*C tail
+  ColCfg cfg = mtb_col_cfg(rows, c, aligned);
+  dim3 grid(cfg.col_blocks, cfg.row_blocks);
+  if (cfg.vec == 4) bn_bwd_partial_kernel<4><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
+  else bn_bwd_partial_kernel<1><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
+  MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
+  bn_bwd_final_kernel<<<mtb_div_up(c, 128), 128, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+                                                          dgamma, dbeta, coef);
+  MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
+  ColCfg s = stream_cfg(rows, c, aligned);
+  dim3 g2(s.col_blocks, s.row_blocks);
+  if (s.vec == 4) bn_bwd_dx_kernel<4><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef);
+  else bn_bwd_dx_kernel<1><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef);
+  MTB_LAUNCH_CHECK("bn_bwd_dx_kernel");
+  return MTB_OK;
+}

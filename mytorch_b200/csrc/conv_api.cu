@@ -1,0 +1,39 @@
+// Public convolution / GEMM entry points.  Each picks the kernel family for the shape: the
+// tcgen05 tensor-core kernels when the shape meets their alignment rules, otherwise the
+// general CUDA-core kernels.  Both families run on the GPU; there is no host fallback.
+#include "common.cuh"
+#include "kernels.h"
+
+MTB_API long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
+  long long a = mtb_conv2d_wgrad_simt_workspace_bytes(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  long long b = mtb_tc_conv2d_workspace_bytes(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  return a > b ? a : b;
+}
+
+MTB_API int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                   const float* wt, const float* bias, float* y, int relu, void* stream) {
+  if (mtb_tc_conv2d_forward_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, y))
+    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
+  return mtb_conv2d_forward_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
+}
+
+MTB_API int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                                 const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream) {
+  if (mtb_tc_conv2d_dgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx))
+    return mtb_tc_conv2d_dgrad_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx, workspace, workspace_bytes, stream);
+  return mtb_conv2d_dgrad_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx, stream);
+}
+
+MTB_API int mtb_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                 const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream) {
+  if (mtb_tc_conv2d_wgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, dy, dw))
+    return mtb_tc_conv2d_wgrad_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, dy, dw, workspace, workspace_bytes, stream);
+  return mtb_conv2d_wgrad_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, dy, dw, workspace, workspace_bytes, stream);
+}
+
+MTB_API int mtb_gemm_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu, float* c,
+                         void* stream) {
+  if (mtb_tc_gemm_supported(m, n, k, a, trans_a, b, trans_b, c))
+    return mtb_tc_gemm_f32(m, n, k, a, trans_a, b, trans_b, bias, relu, c, stream);
+  return mtb_gemm_simt_f32(m, n, k, a, trans_a, b, trans_b, bias, relu, c, stream);
+}

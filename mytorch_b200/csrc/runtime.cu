@@ -1,0 +1,40 @@
+// Library-level state: last error text, device properties.
+#include "common.cuh"
+#include <cstdarg>
+#include <cstring>
+
+static thread_local char g_last_error[512] = "";
+
+int mtb_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_last_error, sizeof(g_last_error), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+int mtb_sm_count() {
+  static int cached[64] = {0};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+MTB_API const char* mtb_last_error() { return g_last_error; }
+
+MTB_API int mtb_version() { return 1; }
+
+// Returns MTB_OK when the current device can run this library (compute capability 10.x).
+MTB_API int mtb_device_check() {
+  int dev = 0, major = 0, minor = 0;
+  MTB_CUDA(cudaGetDevice(&dev));
+  MTB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  MTB_CUDA(cudaDeviceGetAttribute(&minor, cudaDevAttrComputeCapabilityMinor, dev));
+  if (major != 10) return mtb_fail(MTB_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library is built for sm_100a only", dev, major, minor);
+  return MTB_OK;
+}

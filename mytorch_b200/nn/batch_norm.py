@@ -1,0 +1,39 @@
+"""BatchNorm2d (``mytorch/nn/batch_norm.py:7-135``): affine weight=1 / bias=0, running mean 0 /
+running var 1; training mode normalises with batch statistics and blends the *biased* batch
+variance into ``running_var``."""
+from mytorch_b200.dtype import float32
+from mytorch_b200.nn.functional.batch_norm import _batch_norm2d
+from mytorch_b200.nn.module import Module
+from mytorch_b200.nn.parameter import Parameter
+from mytorch_b200.tensor import Tensor
+
+
+class BatchNorm2d(Module):
+    def __init__(self, num_features, eps=1e-5, momentum=0.1, affine=True, track_running_stats=True, device="cpu", dtype=float32):
+        super().__init__()
+        self.num_features, self.eps, self.momentum = num_features, eps, momentum
+        self.affine, self.track_running_stats = affine, track_running_stats
+        if affine:
+            self.weight = Parameter(Tensor(shape=(num_features,), dtype=dtype, device=device))
+            self.bias = Parameter(Tensor(shape=(num_features,), dtype=dtype, device=device))
+        else:
+            self.register_parameter("weight", None)
+            self.register_parameter("bias", None)
+        if track_running_stats:
+            self.running_mean = Tensor(shape=(num_features,), dtype=dtype, device=device)
+            self.running_var = Tensor(shape=(num_features,), dtype=dtype, device=device)
+        else:
+            self.register_buffer("running_mean", None)
+            self.register_buffer("running_var", None)
+        self.reset_parameters()
+
+    def reset_parameters(self):
+        if self.track_running_stats:
+            self.running_mean.fill_(0)
+            self.running_var.fill_(1)
+        if self.affine:
+            self.weight.fill_(1)
+            self.bias.fill_(0)
+
+    def forward(self, x):
+        return _batch_norm2d(x, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean, self.running_var)

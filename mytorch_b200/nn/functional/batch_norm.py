@@ -1,0 +1,22 @@
+"""Fused BatchNorm2d front-end (``mytorch/nn/functional/batch_norm.py:8-51``)."""
+from mytorch_b200.ops._common import dispatch, record, tracker
+from mytorch_b200.tensor import Tensor
+
+
+def _batch_norm2d(input: Tensor, weight, bias, eps, training, momentum, running_mean, running_var):
+    requires_grad = input.requires_grad
+    channels = input.shape[1]
+    if weight is not None and bias is not None:
+        ok = (input.dtype == weight.dtype == bias.dtype and input.device == weight.device == bias.device
+              and weight.shape == (channels,) and bias.shape == (channels,))
+        if not ok:
+            raise RuntimeError("batch_norm2d shape, dtype or device mismatch")
+        requires_grad = requires_grad or weight.requires_grad or bias.requires_grad
+    out, mean, var = dispatch(input.device, "batch_norm2d")(input, weight, bias, eps, training, momentum, running_mean, running_var)
+    out.requires_grad = requires_grad and not tracker.no_grad
+    return record("batch_norm2d", [input, weight, bias, eps], out, [mean, var])
+
+
+@tracker.register_backward_function("batch_norm2d")
+def _batch_norm2d_backward(output_grad, mean, var, input, weight, bias, eps):
+    return dispatch(input.device, "batch_norm2d_backward")(output_grad, mean, var, input, weight, bias, eps)

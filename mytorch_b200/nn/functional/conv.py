@@ -1,0 +1,22 @@
+"""conv2d front-end (``mytorch/nn/functional/conv.py:10-49``)."""
+from mytorch_b200.ops._common import dispatch, grad_enabled, record, tracker
+from mytorch_b200.tensor import MismatchDataTypesError, MismatchDevicesError, Tensor
+
+
+def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0) -> Tensor:
+    tensors = [input, weight] + ([bias] if bias is not None else [])
+    if any(t.device != input.device for t in tensors):
+        raise MismatchDevicesError([t.device for t in tensors])
+    if any(t.dtype != input.dtype for t in tensors):
+        raise MismatchDataTypesError([t.dtype for t in tensors])
+    stride = (stride, stride) if isinstance(stride, int) else tuple(stride)
+    padding = (padding, padding) if isinstance(padding, int) else tuple(padding)
+    out = dispatch(input.device, "conv2d")(input, weight, bias, stride, padding)
+    out.requires_grad = grad_enabled(input, weight, bias)
+    return record("conv2d", [input, weight, bias, stride, padding], out)
+
+
+@tracker.register_backward_function("conv2d")
+def conv2d_backward(output_grad, input, weight, bias, stride, padding):
+    dx, dw, db = dispatch(input.device, "conv2d_backward")(output_grad, input, weight, bias, stride, padding)
+    return [dx, dw, db]

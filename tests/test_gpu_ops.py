@@ -1,0 +1,291 @@
+"""Per-operator parity of the CUDA kernels (through the registry and the C ABI) against the
+NumPy oracle and the golden fixtures from the reference's CPU backend.
+
+Tolerances (relative to the largest reference magnitude): fp32 CUDA-core operators 1e-5;
+convolution / Linear GEMMs (TF32 tensor cores where the shape allows) 5e-3; max-pool values,
+tie masks and argmax indices bit-exact.
+"""
+import numpy as np
+import pytest
+
+from conftest import load_golden, rel_err
+from oracle import ops as O
+
+pytestmark = pytest.mark.gpu
+
+FP32_TOL = 1e-5
+TF32_TOL = 5e-3
+
+
+@pytest.fixture(scope="module")
+def g():
+    import gpu_util
+
+    return gpu_util
+
+
+def _conv_check(g, x, w, b, dy, s, p, ref=None):
+    xt, wt = g.dev(x, True), g.dev(w, True)
+    bt = g.dev(b, True) if b is not None else None
+    y = g.op("conv2d")(xt, wt, bt, (s, s), (p, p))
+    dx, dw, db = g.op("conv2d_backward")(g.dev(dy), xt, wt, bt, (s, s), (p, p))
+    if ref is None:
+        ry = O.conv2d_forward(x, w, b, (s, s), (p, p))
+        rdx, rdw, rdb = O.conv2d_backward(dy, x, w, b is not None, (s, s), (p, p))
+    else:
+        ry, rdx, rdw, rdb = ref
+    assert g.host(y).shape == ry.shape
+    assert rel_err(g.host(y), ry) < TF32_TOL
+    assert rel_err(g.host(dx), rdx) < TF32_TOL
+    assert rel_err(g.host(dw), rdw) < TF32_TOL
+    if b is not None:
+        assert rel_err(g.host(db), rdb) < FP32_TOL * 10
+
+
+def test_conv_golden(g):
+    gd = load_golden("conv")
+    for i in range(int(gd["count"])):
+        n, ci, h, w, co, k, s, p, bias = (int(v) for v in gd[f"c{i}_cfg"])
+        b = gd[f"c{i}_b"] if bias else None
+        ref = (gd[f"c{i}_y"], gd[f"c{i}_dx"], gd[f"c{i}_dw"], gd[f"c{i}_db"] if bias else None)
+        _conv_check(g, gd[f"c{i}_x"], gd[f"c{i}_w"], b, gd[f"c{i}_dy"], s, p, ref)
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, cin, h, w, cout, k, s, p, bias     (shapes of the ResNet / benchmark layers, small batch)
+    (4, 64, 56, 56, 64, 3, 1, 1, True),
+    (8, 64, 32, 32, 64, 3, 1, 1, False),
+    (8, 64, 32, 32, 128, 3, 2, 1, False),
+    (8, 64, 32, 32, 128, 1, 2, 0, False),
+    (8, 128, 16, 16, 128, 3, 1, 1, False),
+    (8, 256, 8, 8, 256, 3, 1, 1, False),
+    (16, 512, 4, 4, 512, 3, 1, 1, False),
+    (8, 3, 32, 32, 64, 3, 1, 1, False),
+    (2, 32, 26, 26, 64, 3, 1, 0, True),
+    (2, 3, 37, 41, 16, 7, 2, 3, False),
+    (3, 20, 9, 11, 24, 3, 1, 1, True),
+])
+def test_conv_oracle(g, cfg):
+    n, ci, h, w, co, k, s, p, bias = cfg
+    rng = np.random.default_rng(hash(cfg) % (2 ** 31))
+    x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((co, ci, k, k)) / np.sqrt(ci * k * k)).astype(np.float32)
+    b = rng.standard_normal(co).astype(np.float32) if bias else None
+    oh, ow = O.conv_out_hw(h, w, k, k, s, p)
+    dy = rng.standard_normal((n, co, oh, ow)).astype(np.float32)
+    _conv_check(g, x, wt, b, dy, s, p)
+
+
+def test_conv_is_deterministic(g):
+    rng = np.random.default_rng(5)
+    x = rng.standard_normal((8, 64, 16, 16)).astype(np.float32)
+    w = rng.standard_normal((64, 64, 3, 3)).astype(np.float32)
+    dy = rng.standard_normal((8, 64, 16, 16)).astype(np.float32)
+    outs = []
+    for _ in range(2):
+        xt, wt = g.dev(x, True), g.dev(w, True)
+        y = g.op("conv2d")(xt, wt, None, (1, 1), (1, 1))
+        dx, dw, _ = g.op("conv2d_backward")(g.dev(dy), xt, wt, None, (1, 1), (1, 1))
+        outs.append((g.host(y), g.host(dx), g.host(dw)))
+    for a, b in zip(*outs):
+        assert np.array_equal(a, b)
+
+
+def test_linear(g):
+    gd = load_golden("misc")
+    x, w, b, dy = g.dev(gd["lin_x"], True), g.dev(gd["lin_w"], True), g.dev(gd["lin_b"], True), g.dev(gd["lin_dy"])
+    y = g.op("linear")(x, w, b)
+    dx, dw, db = g.op("linear_backward")(dy, x, w, b)
+    assert rel_err(g.host(y), gd["lin_y"]) < TF32_TOL and rel_err(g.host(dx), gd["lin_dx"]) < TF32_TOL
+    assert rel_err(g.host(dw), gd["lin_dw"]) < TF32_TOL and rel_err(g.host(db), gd["lin_db"]) < FP32_TOL
+    rng = np.random.default_rng(3)
+    for (bsz, fin, fout) in [(64, 9216, 128), (64, 128, 10), (512, 512, 10), (128, 2048, 1000), (7, 33, 5)]:
+        xa = rng.standard_normal((bsz, fin)).astype(np.float32)
+        wa = (rng.standard_normal((fout, fin)) / np.sqrt(fin)).astype(np.float32)
+        ba = rng.standard_normal(fout).astype(np.float32)
+        da = rng.standard_normal((bsz, fout)).astype(np.float32)
+        x, w, b = g.dev(xa, True), g.dev(wa, True), g.dev(ba, True)
+        y = g.op("linear")(x, w, b)
+        dx, dw, db = g.op("linear_backward")(g.dev(da), x, w, b)
+        rdx, rdw, rdb = O.linear_backward(da, xa, wa, True)
+        assert rel_err(g.host(y), O.linear_forward(xa, wa, ba)) < TF32_TOL
+        assert rel_err(g.host(dx), rdx) < TF32_TOL and rel_err(g.host(dw), rdw) < TF32_TOL
+        assert rel_err(g.host(db), rdb) < FP32_TOL * 10
+
+
+def test_mm_and_permute(g):
+    rng = np.random.default_rng(4)
+    a, b = rng.standard_normal((37, 50)).astype(np.float32), rng.standard_normal((50, 21)).astype(np.float32)
+    dy = rng.standard_normal((37, 21)).astype(np.float32)
+    at, bt = g.dev(a, True), g.dev(b, True)
+    assert rel_err(g.host(g.op("mm")(at, bt)), a @ b) < TF32_TOL
+    da, db = g.op("mm_backward")(g.dev(dy), at, bt)
+    assert rel_err(g.host(da), dy @ b.T) < TF32_TOL and rel_err(g.host(db), a.T @ dy) < TF32_TOL
+    assert np.array_equal(g.host(g.op("permute")(at, (1, 0))), a.T)
+    x4 = rng.standard_normal((2, 3, 4, 5)).astype(np.float32)
+    assert np.array_equal(g.host(g.op("permute")(g.dev(x4), (0, 2, 3, 1))), x4.transpose(0, 2, 3, 1))
+    assert np.array_equal(g.host(g.op("permute_backward")(g.dev(x4.transpose(2, 0, 3, 1).copy()), g.dev(x4), (2, 0, 3, 1))[0]), x4)
+
+
+def test_layout_round_trip_and_reshape(g):
+    rng = np.random.default_rng(6)
+    x = rng.standard_normal((3, 5, 4, 7)).astype(np.float32)
+    xt = g.dev(x)
+    assert np.array_equal(g.host(xt), x)
+    flat = g.op("reshape")(xt, (3, -1))
+    assert flat.shape == (3, 140) and np.array_equal(g.host(flat), x.reshape(3, -1))
+    back = g.op("reshape")(flat, (3, 5, 4, 7))
+    assert np.array_equal(g.host(back), x)
+    assert np.array_equal(g.host(g.op("reshape")(g.dev(x[:, :, :1, :1].copy()), (3, 5))), x[:, :, 0, 0])
+
+
+def test_batch_norm_golden_and_oracle(g):
+    gd = load_golden("batch_norm")
+    for i in range(int(gd["count"])):
+        x, gm, b, rm, rv, dy = (gd[f"b{i}_{k}"] for k in ("x", "g", "b", "rm", "rv", "dy"))
+        xt, gt, bt, rmt, rvt = g.dev(x, True), g.dev(gm, True), g.dev(b, True), g.dev(rm), g.dev(rv)
+        y, mean, var = g.op("batch_norm2d")(xt, gt, bt, 1e-5, True, 0.1, rmt, rvt)
+        assert rel_err(g.host(y), gd[f"b{i}_y"]) < FP32_TOL
+        assert rel_err(g.host(rmt), gd[f"b{i}_rm2"]) < FP32_TOL and rel_err(g.host(rvt), gd[f"b{i}_rv2"]) < FP32_TOL
+        dx, dg, db = g.op("batch_norm2d_backward")(g.dev(dy), mean, var, xt, gt, bt, 1e-5)
+        assert rel_err(g.host(dx), gd[f"b{i}_dx"]) < FP32_TOL * 2
+        assert rel_err(g.host(dg), gd[f"b{i}_dg"]) < FP32_TOL * 2 and rel_err(g.host(db), gd[f"b{i}_db"]) < FP32_TOL * 2
+        ye, _, _ = g.op("batch_norm2d")(g.dev(x), g.dev(gm), g.dev(b), 1e-5, False, 0.1, g.dev(rm), g.dev(rv))
+        assert rel_err(g.host(ye), gd[f"b{i}_yeval"]) < FP32_TOL
+    rng = np.random.default_rng(7)
+    for shp in [(16, 128, 28, 28), (32, 64, 32, 32), (8, 512, 4, 4), (5, 24, 9, 9), (4, 7, 6, 6)]:
+        c = shp[1]
+        x = (0.5 + 2.0 * rng.standard_normal(shp)).astype(np.float32)
+        gm, b = rng.uniform(0.5, 1.5, c).astype(np.float32), rng.standard_normal(c).astype(np.float32)
+        dy = rng.standard_normal(shp).astype(np.float32)
+        ry, rmean, rvar, rrm, rrv = O.batch_norm2d_forward(x, gm, b, 1e-5, True, 0.1, np.zeros(c, np.float32), np.ones(c, np.float32))
+        rdx, rdg, rdb = O.batch_norm2d_backward(dy, rmean, rvar, x, gm, 1e-5)
+        xt, gt, bt, rmt, rvt = g.dev(x, True), g.dev(gm, True), g.dev(b, True), g.dev(np.zeros(c, np.float32)), g.dev(np.ones(c, np.float32))
+        y, mean, var = g.op("batch_norm2d")(xt, gt, bt, 1e-5, True, 0.1, rmt, rvt)
+        dx, dg, db = g.op("batch_norm2d_backward")(g.dev(dy), mean, var, xt, gt, bt, 1e-5)
+        assert rel_err(g.host(y), ry) < FP32_TOL and rel_err(g.host(mean), rmean.reshape(-1)) < FP32_TOL
+        assert rel_err(g.host(var), rvar.reshape(-1)) < FP32_TOL
+        assert rel_err(g.host(rmt), rrm) < FP32_TOL and rel_err(g.host(rvt), rrv) < FP32_TOL
+        assert rel_err(g.host(dx), rdx) < FP32_TOL * 2 and rel_err(g.host(dg), rdg) < FP32_TOL * 3 and rel_err(g.host(db), rdb) < FP32_TOL * 3
+
+
+def test_max_pool_bit_exact(g):
+    from mytorch_b200.backends.cuda.ops import max_pool2d_argmax
+
+    gd = load_golden("max_pool")
+    for i in range(int(gd["count"])):
+        k, s, p, _ = (int(v) for v in gd[f"p{i}_cfg"])
+        x, dy = gd[f"p{i}_x"], gd[f"p{i}_dy"]
+        xt = g.dev(x, True)
+        y = g.op("max_pool2d")(xt, (k, k), (s, s), (p, p))
+        assert np.array_equal(g.host(y), gd[f"p{i}_y"])
+        assert np.array_equal(max_pool2d_argmax(y), O.max_pool2d_argmax(x, k, s, p).astype(np.uint8))
+        (dx,) = g.op("max_pool2d_backward")(g.dev(dy), y, xt, (k, k), (s, s), (p, p))
+        assert rel_err(g.host(dx), gd[f"p{i}_dx"]) < 1e-6
+        y._pool_tiemask = None  # force the x == out recomputation path
+        (dx2,) = g.op("max_pool2d_backward")(g.dev(dy), y, xt, (k, k), (s, s), (p, p))
+        assert np.array_equal(g.host(dx2), g.host(dx))
+    rng = np.random.default_rng(8)
+    for shp, k, s, p in [((8, 128, 56, 56), 2, 2, 0), ((4, 64, 112, 112), 3, 2, 1), ((2, 6, 9, 9), 5, 2, 2), ((3, 5, 7, 7), 2, 2, 0)]:
+        x = rng.standard_normal(shp).astype(np.float32)
+        xt = g.dev(x, True)
+        y = g.op("max_pool2d")(xt, (k, k), (s, s), (p, p))
+        ry = O.max_pool2d_forward(x, k, s, p)
+        assert np.array_equal(g.host(y), ry)
+        dy = rng.standard_normal(ry.shape).astype(np.float32)
+        (dx,) = g.op("max_pool2d_backward")(g.dev(dy), y, xt, (k, k), (s, s), (p, p))
+        assert rel_err(g.host(dx), O.max_pool2d_backward(dy, ry, x, k, s, p)) < 1e-6
+        if k * k <= 16:
+            assert np.array_equal(max_pool2d_argmax(y), O.max_pool2d_argmax(x, k, s, p).astype(np.uint8))
+
+
+def test_elementwise_and_reductions(g):
+    gd = load_golden("misc")
+    assert np.array_equal(g.host(g.op("relu")(g.dev(gd["relu_x"]))), gd["relu_y"])
+    assert np.array_equal(g.host(g.op("relu_backward")(g.dev(gd["relu_dy"]), g.dev(gd["relu_x"]))[0]), gd["relu_dx"])
+    a, b = g.dev(gd["add_a"], True), g.dev(gd["add_b"], True)
+    assert np.array_equal(g.host(g.op("add")(a, b, 1)), gd["add_y"])
+    da, db = g.op("add_backward")(g.dev(gd["add_dy"]), a, b, 1)
+    assert np.array_equal(g.host(da), gd["add_da"]) and np.array_equal(g.host(db), gd["add_db"])
+    a, b = g.dev(gd["badd_a"], True), g.dev(gd["badd_b"], True)
+    assert np.array_equal(g.host(g.op("add")(a, b, 1)), gd["badd_y"])
+    da, db = g.op("add_backward")(g.dev(gd["badd_dy"]), a, b, 1)
+    assert np.array_equal(g.host(da), gd["badd_da"]) and rel_err(g.host(db), gd["badd_db"]) < FP32_TOL
+    x = g.dev(gd["gap_x"], True)
+    assert rel_err(g.host(g.op("sum_scale")(x, (2, 3), False, 1 / 16)), gd["gap_y"]) < FP32_TOL
+    assert rel_err(g.host(g.op("sum_scale_backward")(g.dev(gd["gap_dy"]), x, (2, 3), False, 1 / 16)[0]), gd["gap_dx"]) < FP32_TOL
+    assert rel_err(g.host(g.op("sum_scale")(x, (0, 2, 3), False, 1)), gd["csum_y"]) < FP32_TOL
+    assert rel_err(g.host(g.op("sum_scale_backward")(g.dev(gd["csum_dy"]), x, (0, 2, 3), False, 1)[0]), gd["csum_dx"]) < FP32_TOL
+    xs = gd["gap_x"]
+    for dim, keep in [((1,), False), ((0, 1, 2, 3), False), ((3,), True), ((0,), True), ((1, 2), False)]:
+        r = O.sum_scale_forward(xs, dim, keep, 0.5)
+        out = g.op("sum_scale")(x, dim, keep, 0.5)
+        assert out.shape == r.shape and rel_err(g.host(out), r) < FP32_TOL
+        dyv = np.random.default_rng(9).standard_normal(r.shape).astype(np.float32)
+        dxv = g.op("sum_scale_backward")(g.dev(dyv), x, dim, keep, 0.5)[0]
+        assert rel_err(g.host(dxv), O.sum_scale_backward(dyv, xs.shape, dim, keep, 0.5)) < FP32_TOL
+    rng = np.random.default_rng(10)
+    p, q = rng.standard_normal((4, 3, 5, 5)).astype(np.float32), rng.standard_normal((1, 3, 1, 1)).astype(np.float32)
+    for name, f in [("add", lambda u, v: u + 2 * v), ("sub", lambda u, v: u - 2 * v)]:
+        assert rel_err(g.host(g.op(name)(g.dev(p), g.dev(q), 2)), f(p, q)) < FP32_TOL
+    assert rel_err(g.host(g.op("mul")(g.dev(p), g.dev(q))), p * q) < FP32_TOL
+    assert rel_err(g.host(g.op("div")(g.dev(p), g.dev(np.abs(q) + 1))), p / (np.abs(q) + 1)) < FP32_TOL
+    dp, dq = g.op("mul_backward")(g.dev(p), g.dev(p, True), g.dev(q, True))
+    rp, rq = O.mul_backward(p, p, q)
+    assert rel_err(g.host(dp), rp) < FP32_TOL and rel_err(g.host(dq), rq) < FP32_TOL
+
+
+def test_cross_entropy(g):
+    gd = load_golden("misc")
+    z, t = g.dev(gd["ce_z"], True), g.dev(gd["ce_t"])
+    loss = g.op("cross_entropy")(z, t)
+    assert loss.shape == (1,) and rel_err(g.host(loss), gd["ce_loss"]) < FP32_TOL
+    (dz,) = g.op("cross_entropy_backward")(g.dev(np.ones(1, np.float32)), z, t)
+    assert rel_err(g.host(dz), gd["ce_dz"]) < FP32_TOL
+    rng = np.random.default_rng(11)
+    for b, c in [(512, 10), (128, 1000), (3, 37)]:
+        za, ta = (4 * rng.standard_normal((b, c))).astype(np.float32), rng.integers(0, c, b).astype(np.int64)
+        zt = g.dev(za, True)
+        assert rel_err(g.host(g.op("cross_entropy")(zt, g.dev(ta))), O.cross_entropy_forward(za, ta)) < FP32_TOL
+        (dz,) = g.op("cross_entropy_backward")(g.dev(np.full(1, 0.7, np.float32)), zt, g.dev(ta))
+        assert rel_err(g.host(dz), O.cross_entropy_backward(np.float32(0.7), za, ta)) < FP32_TOL
+
+
+def test_sgd(g):
+    import mytorch_b200 as mt
+    import mytorch_b200.nn as nn
+    from mytorch_b200.optim import SGD
+
+    gd = load_golden("misc")
+    cfgs = [dict(lr=0.1, momentum=0.9), dict(lr=0.05, momentum=0.8, nesterov=True, weight_decay=1e-2),
+            dict(lr=0.01, momentum=0.5, dampening=0.3, maximize=True)]
+    for i, kw in enumerate(cfgs):
+        for multi in (True, False):
+            p = nn.Parameter(g.dev(gd[f"sgd{i}_p0"].copy()))
+            opt = SGD([p], **kw)
+            for gname, pname in (("g1", "p1"), ("g2", "p2")):
+                p.grad = g.dev(gd[f"sgd{i}_{gname}"])
+                if multi:
+                    opt.step()
+                else:
+                    st = opt.state.setdefault(p, {})
+                    first = "momentum_buffer" not in st
+                    if first:
+                        st["momentum_buffer"] = mt.Tensor(shape=p.shape, device=p.device, dtype=p.dtype)
+                    g.op("sgd")(p, st["momentum_buffer"], first, kw["lr"], kw.get("weight_decay", 0), kw["momentum"],
+                                kw.get("dampening", 0), kw.get("nesterov", False), kw.get("maximize", False))
+                assert rel_err(g.host(p.detach()), gd[f"sgd{i}_{pname}"]) < FP32_TOL
+            assert rel_err(g.host(opt.state[p]["momentum_buffer"]), gd[f"sgd{i}_buf"]) < FP32_TOL
+
+
+def test_errors_are_python_exceptions(g):
+    import mytorch_b200 as mt
+
+    x = g.dev(np.zeros((1, 3, 8, 8), np.float32))
+    w = g.dev(np.zeros((4, 5, 3, 3), np.float32))
+    with pytest.raises(RuntimeError):
+        g.op("conv2d")(x, w, None, (1, 1), (0, 0))
+    with pytest.raises(RuntimeError):
+        g.op("cross_entropy")(g.dev(np.zeros((2, 3), np.float32)), g.dev(np.zeros(2, np.int32)))
+    with pytest.raises(RuntimeError):
+        mt.tensor(np.zeros(3, np.int64), device="cuda:0", requires_grad=True)

@@ -1,0 +1,132 @@
+"""Host-side behaviour that needs no GPU: tensor / device / module / optimizer semantics of the
+reference API, seeded initialisation, and the C-ABI library's exported symbols."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+import mytorch_b200 as mt
+import mytorch_b200.nn as nn
+from conftest import ROOT, load_golden
+from mytorch_b200.optim import SGD
+from mytorch_b200.tensor import Device
+
+
+def test_device_parsing_and_equality():
+    assert Device("cuda:1").type == "cuda" and Device("cuda:1").index == 1
+    assert Device(" cpu ").index is None and repr(Device("cuda:0")) == "cuda:0"
+    assert Device("cuda:0") == Device(Device("cuda:0")) and Device("cuda") != Device("cuda:0")
+
+
+def test_tensor_constructor_rules():
+    t = mt.tensor([[1, 2], [3, 4]], dtype=mt.float32)
+    assert t.shape == (2, 2) and t.dtype is mt.float32 and t.device == Device("cpu")
+    assert mt.Tensor(shape=(2, 3), dtype=mt.int64)._numpy().sum() == 0
+    with pytest.raises(RuntimeError):
+        mt.tensor([1, 2], dtype=mt.int64, requires_grad=True)
+    with pytest.raises(RuntimeError):
+        mt.Tensor(cpu_array=np.zeros(3, np.float32), dtype=mt.float64)
+    with pytest.raises(RuntimeError):
+        mt.Tensor(cpu_array=np.zeros(3, np.float32), shape=(4,))
+    g = mt.tensor([1.0], dtype=mt.float32, requires_grad=True)
+    with pytest.raises(RuntimeError):
+        g.numpy()
+    assert g.detach().numpy()[0] == 1.0 and g.item() == 1.0
+    assert "tensor(" in repr(g)
+
+
+def test_no_cpu_compute_backend():
+    x = mt.tensor(np.zeros((1, 1, 4, 4), np.float32))
+    conv = nn.Conv2d(1, 2, 3)
+    with pytest.raises(RuntimeError, match="no function registered for conv2d on cpu"):
+        conv(x)
+
+
+def test_seeded_init_matches_reference_fixture():
+    g = load_golden("misc")
+    mt.manual_seed(77)
+    c, l = nn.Conv2d(3, 4, 3), nn.Linear(6, 5)
+    assert np.array_equal(c.weight._numpy(), g["init_cw"]) and np.array_equal(c.bias._numpy(), g["init_cb"])
+    assert np.array_equal(l.weight._numpy(), g["init_lw"]) and np.array_equal(l.bias._numpy(), g["init_lb"])
+
+
+def test_module_registration_and_state_dict(tmp_path):
+    from mytorch_b200.examples.models import ResNet18Cifar
+
+    mt.manual_seed(1)
+    net = ResNet18Cifar(widths=(4, 8, 8, 8))
+    keys = list(net.state_dict().keys())
+    assert keys[:6] == ["conv1.weight", "bn1.weight", "bn1.bias", "bn1.running_mean", "bn1.running_var",
+                        "layer1.0.conv1.weight"]
+    assert "layer2.0.downsample.0.weight" in keys and keys[-2:] == ["fc.weight", "fc.bias"]
+    assert len(list(net.parameters())) == 62
+    assert net.training and not net.eval().training and all(not m.training for _, m in net.named_modules())
+    path = os.path.join(tmp_path, "ckpt.bin")
+    mt.save(net.state_dict(), path)
+    mt.manual_seed(2)
+    other = ResNet18Cifar(widths=(4, 8, 8, 8))
+    assert not np.array_equal(other.fc.weight._numpy(), net.fc.weight._numpy())
+    other.load_state_dict(mt.load(path))
+    for (k1, a), (k2, b) in zip(net.state_dict().items(), other.state_dict().items()):
+        assert k1 == k2 and np.array_equal(a._numpy(), b._numpy())
+
+
+def test_optimizer_groups_and_state():
+    p, q = nn.Parameter(mt.tensor(np.ones(3, np.float32))), nn.Parameter(mt.tensor(np.ones(2, np.float32)))
+    opt = SGD([{"params": [p], "lr": 0.5}, {"params": [q]}], lr=0.1, momentum=0.9)
+    assert opt.param_groups[0]["lr"] == 0.5 and opt.param_groups[1]["lr"] == 0.1 and opt.param_groups[1]["momentum"] == 0.9
+    with pytest.raises(RuntimeError):
+        SGD([{"params": [p]}, {"params": [p]}])
+    p.grad = mt.tensor(np.ones(3, np.float32))
+    opt.zero_grad()
+    assert p.grad is None
+    sd = opt.state_dict()
+    assert sd["param_groups"][0]["params"] == [id(p)]
+
+
+def test_backward_requires_graph_and_scalar():
+    t = mt.tensor([1.0, 2.0], dtype=mt.float32, requires_grad=True)
+    with pytest.raises(RuntimeError, match="backward a tensor twice"):
+        t.backward()
+    with mt.no_grad():
+        with mt.no_grad():
+            pass
+        from mytorch_b200.autograd import DAGTracker
+
+        assert DAGTracker.instance().no_grad
+    assert not DAGTracker.instance().no_grad
+
+
+def _declared_symbols():
+    text = open(os.path.join(ROOT, "include", "mytorch_b200.h")).read()
+    return sorted(set(re.findall(r"\b(mtb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    from mytorch_b200.backends.cuda.env import LIBRARY_PATH, _SIGNATURES
+
+    if not os.path.exists(LIBRARY_PATH):
+        from mytorch_b200.build import build_library
+
+        build_library()
+    dll = ctypes.CDLL(LIBRARY_PATH)
+    names = _declared_symbols()
+    assert len(names) >= 35
+    for name in names:
+        assert hasattr(dll, name), f"{name} is declared in include/mytorch_b200.h but not exported"
+    for name in _SIGNATURES:
+        assert name in names, f"{name} is bound by the Python layer but not declared in the header"
+    dll.mtb_version.restype = ctypes.c_int
+    assert dll.mtb_version() >= 1
+
+
+def test_shard_bounds_cover_batch():
+    from mytorch_b200.parallel import shard_bounds
+
+    for n in (512, 10, 7):
+        for world in (1, 2, 4, 8):
+            spans = [shard_bounds(n, r, world) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == n
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
