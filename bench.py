@@ -1,0 +1,401 @@
+"""Benchmark: ResNet-18 (CIFAR variant) training step, global batch 512, fp32 storage with TF32
+tensor-core convolutions, SGD lr 0.1 momentum 0.9, data-parallel over N GPUs (one process each).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+
+Under torchrun (N > 1) every rank runs this file; rank 0 prints ONE JSON line.  Synthetic
+3x32x32 images ~ N(0,1) and uniform labels stand in for CIFAR-10 (no dataset is read).
+
+`value`  : images/s with the batch already resident in device memory (whole job, all ranks).
+`e2e`    : the same step fed from pinned host memory each iteration (H2D of images + labels,
+           D2H of the loss) through the package's public API.
+`roofline`: the dominant kernel timed alone with CUDA events on its launch stream.
+`cpu_baseline` / `--impl reference`: the NumPy oracle (a restatement of the reference's CPU
+backend) timed on the host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+GLOBAL_BATCH = 512
+SEED = 1003
+WORKLOAD = "configs[3]: ResNet-18 CIFAR variant, full training step (fwd+bwd+SGD momentum), global batch 512, 3x32x32"
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": p["hbm_gbs"], "bf16_tflops": p["bf16_tflops"], "bf16_tflops_sustained": p.get("bf16_tflops_sustained"),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.proc, self.path = index, None, f"/tmp/mtb_clocks_{os.getpid()}.csv"
+
+    def start(self):
+        try:
+            self.out = open(self.path, "w")
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                                          "-i", str(self.index)], stdout=self.out, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        self.proc.wait()
+        self.out.close()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in open(self.path):
+            f = [s.strip() for s in line.split(",")]
+            if len(f) < 8:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(names, f[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def conv_flops_resnet18(batch):
+    """Algorithmic FLOPs (2*M*N*K per GEMM) of every conv and the fc layer, forward only."""
+    total, hw, cin = 0, 32, 3
+    total += 2 * batch * hw * hw * 64 * cin * 9
+    cin = 64
+    for si, wd in enumerate((64, 128, 256, 512)):
+        for bi in range(2):
+            stride = 2 if (si > 0 and bi == 0) else 1
+            hw_out = hw // stride
+            total += 2 * batch * hw_out * hw_out * wd * cin * 9
+            total += 2 * batch * hw_out * hw_out * wd * wd * 9
+            if stride != 1 or cin != wd:
+                total += 2 * batch * hw_out * hw_out * wd * cin
+            cin, hw = wd, hw_out
+    total += 2 * batch * 512 * 10
+    return total
+
+
+# --------------------------------------------------------------------------- reference / CPU arm
+
+def cpu_reference_step(sample_batch, steps, warmup):
+    """The NumPy oracle's ResNet-18 step on `sample_batch` images, all host threads."""
+    from oracle import models as OM
+
+    rng = np.random.default_rng(SEED)
+    x = rng.standard_normal((sample_batch, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, sample_batch).astype(np.int64)
+    net = OM.resnet18_cifar(SEED)
+    for _ in range(warmup):
+        net.train_step(x, t, 0.1, 0.9)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        net.train_step(x, t, 0.1, 0.9)
+    dt = (time.perf_counter() - t0) / steps
+    return sample_batch / dt, dt
+
+
+def blas_threads():
+    try:
+        from threadpoolctl import threadpool_info
+
+        return max([p.get("num_threads", 1) for p in threadpool_info()] or [1])
+    except Exception:
+        return os.cpu_count() or 1
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    sample = 16
+    ips, dt = cpu_reference_step(sample, max(1, min(args.steps, 3)), max(1, min(args.warmup, 1)))
+    line = {
+        "impl": "reference", "metric": "train_images_per_sec", "value": ips, "unit": "images/s", "n_gpus": args.gpus,
+        "steps": max(1, min(args.steps, 3)), "warmup": max(1, min(args.warmup, 1)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f64/f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "parallelism": "cpu"},
+        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": blas_threads(), "kind": "port",
+                         "sample": f"one full training step of the same ResNet-18 at batch {sample} (NumPy restatement of the "
+                                   "reference CPU backend; the reference is Python and is not present on this box)"},
+        "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line))
+
+
+# --------------------------------------------------------------------------- GPU arm
+
+def kernel_legs(torch, env, peaks):
+    """Time the dominant kernels alone (CUDA events on the launch stream, buffers rotated so that
+    every launch reads data that is not in L2).  Returns (roofline dict, per-kernel dict)."""
+    import mytorch_b200 as mt
+    from mytorch_b200.backends.backend_dispatcher import BackendDispatcher
+
+    op = lambda name: BackendDispatcher.instance().dispatch("cuda", name)
+    rng = np.random.default_rng(1)
+    stream = torch.cuda.current_stream()
+
+    def timed(fn, reps=10, warm=3):
+        for i in range(warm):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(reps):
+            fn(i)
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / reps * 1e-3
+
+    out = {}
+    # dominant conv layer of the step: 64->64 3x3 on 32x32 at the full batch (4 of the 20 convs, 27% of the FLOPs)
+    n = GLOBAL_BATCH
+    sets = []
+    for _ in range(3):  # 3 x (134 MB in + 134 MB out) > 126 MB L2
+        x = mt.tensor(rng.standard_normal((n, 64, 32, 32)).astype(np.float32), device="cuda", requires_grad=True)
+        dy = mt.tensor(rng.standard_normal((n, 64, 32, 32)).astype(np.float32), device="cuda")
+        sets.append((x, dy))
+    w = mt.tensor((rng.standard_normal((64, 64, 3, 3)) / 24).astype(np.float32), device="cuda", requires_grad=True)
+    flops = 2.0 * n * 32 * 32 * 64 * 64 * 9
+    t_f = timed(lambda i: op("conv2d")(sets[i % 3][0], w, None, (1, 1), (1, 1)))
+    w.requires_grad = False
+    t_d = timed(lambda i: op("conv2d_backward")(sets[i % 3][1], sets[i % 3][0], w, None, (1, 1), (1, 1)))
+    w.requires_grad = True
+    for x, _ in sets:
+        x.requires_grad = False
+    t_w = timed(lambda i: op("conv2d_backward")(sets[i % 3][1], sets[i % 3][0], w, None, (1, 1), (1, 1)))
+    tf32_peak = peaks["bf16_tflops"] / 2
+    out["conv3x3_64_fwd_tflops"] = flops / t_f / 1e12
+    out["conv3x3_64_dgrad_tflops"] = flops / t_d / 1e12
+    out["conv3x3_64_wgrad_tflops"] = flops / t_w / 1e12
+    # BatchNorm forward (3S) / backward (5S) and ReLU on the same activation shape
+    x, dy = sets[0]
+    S = 4.0 * n * 64 * 32 * 32
+    gamma = mt.tensor(np.ones(64, np.float32), device="cuda", requires_grad=True)
+    beta = mt.tensor(np.zeros(64, np.float32), device="cuda", requires_grad=True)
+    rm, rv = mt.tensor(np.zeros(64, np.float32), device="cuda"), mt.tensor(np.ones(64, np.float32), device="cuda")
+    res = {}
+
+    def bn_f(i):
+        res["y"], res["m"], res["v"] = op("batch_norm2d")(sets[i % 3][0], gamma, beta, 1e-5, True, 0.1, rm, rv)
+
+    t = timed(bn_f)
+    out["bn_fwd_gbs"] = 3 * S / t / 1e9
+    t = timed(lambda i: op("batch_norm2d_backward")(sets[i % 3][1], res["m"], res["v"], sets[i % 3][0], gamma, beta, 1e-5))
+    out["bn_bwd_gbs"] = 5 * S / t / 1e9
+    t = timed(lambda i: op("relu")(sets[i % 3][0]))
+    out["relu_fwd_gbs"] = 2 * S / t / 1e9
+    roof = {"bound": "tensor", "kernel": "conv2d forward 64->64 3x3 s1 p1 on 512x32x32 (dominant layer shape of the step)",
+            "achieved": out["conv3x3_64_fwd_tflops"], "peak": tf32_peak, "unit": "TFLOP/s", "frac": out["conv3x3_64_fwd_tflops"] / tf32_peak,
+            "traffic": None,
+            "peak_note": f"TF32 dense = half of the {peaks['source']} bf16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
+                         f"HBM figures in `kernels` are against {peaks['hbm_gbs']} GB/s ({peaks['source']})"}
+    out["hbm_frac"] = {k: out[k] / peaks["hbm_gbs"] for k in ("bn_fwd_gbs", "bn_bwd_gbs", "relu_fwd_gbs")}
+    return roof, out
+
+
+def run_gpu_arm(args):
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            sys.exit(f"--gpus {args.gpus} needs torchrun: python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...")
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+
+    import mytorch_b200 as mt
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.backends.cuda.env import CudaEnv
+    from mytorch_b200.cuda_graph import StepGraph
+    from mytorch_b200.examples.models import ResNet18Cifar
+    from mytorch_b200.optim import SGD
+    from mytorch_b200.parallel import DataParallel, shard_bounds
+
+    env = CudaEnv.instance()
+    dev = f"cuda:{local}"
+    peaks = measured_peaks()
+
+    rng = np.random.default_rng(SEED)
+    x_all = rng.standard_normal((GLOBAL_BATCH, 3, 32, 32)).astype(np.float32)
+    t_all = rng.integers(0, 10, GLOBAL_BATCH).astype(np.int64)
+    lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
+    local_batch = hi - lo
+    # a few distinct host batches in pinned memory for the end-to-end leg
+    host_x = [torch.from_numpy(np.roll(x_all, s, axis=0)[lo:hi].copy()).pin_memory() for s in range(4)]
+    host_t = [torch.from_numpy(np.roll(t_all, s, axis=0)[lo:hi].copy()).pin_memory() for s in range(4)]
+
+    mt.manual_seed(SEED)
+    net = ResNet18Cifar()
+    net.to(dev)
+    dp = DataParallel(net)
+    opt = SGD(net.parameters(), lr=0.1, momentum=0.9)
+    xs = mt.tensor(x_all[lo:hi], device=dev)
+    ts = mt.tensor(t_all[lo:hi], device=dev)
+
+    def step():
+        loss = F.cross_entropy(dp(xs), ts)
+        opt.zero_grad()
+        loss.backward()
+        dp.reduce_gradients()
+        opt.step()
+        return loss
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize()
+
+    first_loss = step().item()
+    step()
+    runner = None
+    if not args.no_graph:
+        before = env.lib.launches
+        sg = StepGraph(step, [xs, ts])
+        sg.capture()
+        calls_per_step = env.lib.launches - before
+        runner = sg
+    else:
+        before = env.lib.launches
+        step()
+        calls_per_step = env.lib.launches - before
+
+    def run_resident():
+        if runner is not None:
+            runner.replay()
+        else:
+            step()
+
+    def run_e2e(i):
+        if runner is not None:
+            return runner.replay([host_x[i % 4], host_t[i % 4]]).item()
+        from mytorch_b200.backends.cuda.ops import upload_into
+
+        upload_into(xs, host_x[i % 4])
+        upload_into(ts, host_t[i % 4])
+        return step().item()
+
+    stream = torch.cuda.current_stream()
+
+    def timed_region(body, steps):
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for i in range(steps):
+            body(i)
+        e1.record(stream)
+        barrier()
+        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        if world > 1:
+            dist.all_reduce(ms, op=dist.ReduceOp.MAX)
+        return float(ms.item())
+
+    for _ in range(max(args.warmup, 3)):
+        run_resident()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    total_ms = timed_region(lambda i: run_resident(), args.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    for i in range(2):
+        run_e2e(i)
+    e2e_ms = timed_region(run_e2e, args.steps)
+    last_loss = run_e2e(0)
+
+    ms_per_step = total_ms / args.steps
+    value = GLOBAL_BATCH / (ms_per_step * 1e-3)
+    e2e_value = GLOBAL_BATCH / (e2e_ms / args.steps * 1e-3)
+    step_flops = 3 * conv_flops_resnet18(GLOBAL_BATCH) - 2 * GLOBAL_BATCH * 32 * 32 * 64 * 27  # stem dgrad is not executed
+
+    roof, kernels, cpu = None, None, None
+    if rank == 0 and world == 1 and not args.skip_legs:
+        roof, kernels = kernel_legs(torch, env, peaks)
+        try:
+            a = torch.randn(8192, 8192, device=dev)
+            b = torch.randn(8192, 8192, device=dev)
+            torch.backends.cuda.matmul.allow_tf32 = True
+            best = 1e9
+            for _ in range(6):
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                torch.matmul(a, b)
+                e1.record()
+                torch.cuda.synchronize()
+                best = min(best, e0.elapsed_time(e1))
+            kernels["cublas_tf32_8192_tflops"] = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
+        except Exception as e:  # measurement aid only
+            kernels["cublas_tf32_8192_tflops"] = f"unavailable: {e}"
+        ips, dt = cpu_reference_step(16, 1, 1)
+        cpu = {"value": ips, "unit": "images/s", "cores": blas_threads(), "kind": "port",
+               "sample": "one full ResNet-18 training step at batch 16 with the NumPy restatement of the reference CPU backend"}
+
+    if rank == 0:
+        line = {
+            "metric": "train_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
+            "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "tf32 (fp32 storage, fp32 accumulate)", "data": "synthetic",
+            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_batch, "parallelism": f"dp{world}",
+                       "cuda_graph": not args.no_graph,
+                       "l2": "no flush: one step streams ~1.3 GB of activations per pass, 10x the 126 MB L2"},
+            "step_tflops": step_flops / (ms_per_step * 1e-3) / 1e12,
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_t[0].numel() * 8) * world,
+                    "d2h_bytes_per_step": 4 * world},
+            "gpu_launches": calls_per_step * args.steps,
+            "gpu_launches_note": "C-ABI calls per step x steps; each call enqueues 1-3 kernels of libmytorch_b200.so",
+            "loss_first": first_loss, "loss_last": last_loss,
+            "clocks": clocks, "roofline": roof, "kernels": kernels, "cpu_baseline": cpu,
+        }
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference_arm(args)
+    else:
+        run_gpu_arm(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,205 @@
+"""Whole training steps on the GPU against the golden summaries from the reference's CPU
+backend and against the NumPy oracle: the small MNIST-shaped CNN, ResNet-18 (CIFAR variant),
+and the BatchNorm -> ReLU -> MaxPool block.  Losses and gradients within 5e-3 relative
+(TF32 tensor-core convolutions); pooled values and argmax bit-exact."""
+import numpy as np
+import pytest
+
+from conftest import load_golden, rel_err, summarize
+from oracle import models as OM
+
+pytestmark = pytest.mark.gpu
+
+TOL = 5e-3
+
+
+def _check_summary(gd, prefix, named, tol):
+    worst = 0.0
+    for name, arr in named:
+        stats, sample = summarize(arr)
+        ref = gd[f"{prefix}/{name}/sample"]
+        scale = max(np.max(np.abs(ref)), 1e-30)
+        err = np.max(np.abs(sample - ref)) / scale
+        worst = max(worst, err)
+        assert err < tol, (prefix, name, err)
+        rn = gd[f"{prefix}/{name}/stats"][2]
+        assert abs(stats[2] - rn) <= tol * max(rn, 1e-30), (prefix, name, stats[2], rn)
+    return worst
+
+
+def _train(net, x, t, lr, momentum, steps, gd, tag, tol=TOL):
+    import gpu_util as g
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.optim import SGD
+
+    net.to(g.DEV)
+    opt = SGD(net.parameters(), lr=lr, momentum=momentum)
+    _check_summary(gd, f"{tag}/init", [(k, g.host(v.detach())) for k, v in net.named_parameters()], 1e-7)
+    xt, tt = g.dev(x), g.dev(t)
+    losses = []
+    for s in range(steps):
+        loss = F.cross_entropy(net(xt), tt)
+        opt.zero_grad()
+        loss.backward()
+        _check_summary(gd, f"{tag}/grad{s}", [(k, g.host(v.grad)) for k, v in net.named_parameters()], tol)
+        opt.step()
+        _check_summary(gd, f"{tag}/param{s}", [(k, g.host(v.detach())) for k, v in net.named_parameters()], tol)
+        losses.append(loss.item())
+        assert abs(losses[-1] - gd[f"{tag}/losses"][s]) < tol * abs(gd[f"{tag}/losses"][s])
+    _check_summary(gd, f"{tag}/buffers", [(k, g.host(v)) for k, v in net.named_buffers()], tol)
+    return losses
+
+
+def test_small_cnn_two_steps_match_reference():
+    import mytorch_b200 as mt
+    from mytorch_b200.examples.models import small_cnn
+
+    gd = load_golden("models")
+    rng = np.random.default_rng(1000)
+    x = rng.standard_normal((64, 1, 28, 28)).astype(np.float32)
+    t = rng.integers(0, 10, 64).astype(np.int64)
+    mt.manual_seed(1000)
+    _train(small_cnn(), x, t, 0.01, 0.9, 2, gd, "cnn")
+
+
+def test_resnet18_reduced_width_two_steps_match_reference():
+    import mytorch_b200 as mt
+    from mytorch_b200.examples.models import ResNet18Cifar
+
+    gd = load_golden("models")
+    rng = np.random.default_rng(1003)
+    x = rng.standard_normal((8, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, 8).astype(np.int64)
+    mt.manual_seed(1003)
+    _train(ResNet18Cifar((8, 16, 32, 64)), x, t, 0.1, 0.9, 2, gd, "resnet_w8", tol=2e-2)
+
+
+def test_resnet18_full_width_step_matches_reference():
+    import mytorch_b200 as mt
+    from mytorch_b200.examples.models import ResNet18Cifar
+
+    gd = load_golden("models")
+    rng = np.random.default_rng(1004)
+    x = rng.standard_normal((4, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, 4).astype(np.int64)
+    mt.manual_seed(1004)
+    _train(ResNet18Cifar(), x, t, 0.1, 0.9, 1, gd, "resnet_full", tol=2e-2)
+
+
+def test_resnet18_batch64_step_matches_oracle():
+    """A larger batch than the fixtures hold: the oracle replays the same step on the CPU."""
+    import gpu_util as g
+    import mytorch_b200 as mt
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.examples.models import ResNet18Cifar
+    from mytorch_b200.optim import SGD
+
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((32, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, 32).astype(np.int64)
+    ref = OM.resnet18_cifar(55, (16, 32, 64, 128))
+    rloss, rgrads = ref.train_step(x, t, 0.1, 0.9)
+    mt.manual_seed(55)
+    net = ResNet18Cifar((16, 32, 64, 128))
+    net.to(g.DEV)
+    opt = SGD(net.parameters(), lr=0.1, momentum=0.9)
+    loss = F.cross_entropy(net(g.dev(x)), g.dev(t))
+    opt.zero_grad()
+    loss.backward()
+    assert abs(loss.item() - rloss) < TOL * abs(rloss)
+    named = dict(net.named_parameters())
+    for name, rg in rgrads.items():
+        key = name.replace("conv1.", "conv1.", 1)
+        assert rel_err(g.host(named[key].grad), rg) < 2e-2, name
+    opt.step()
+    for name, layer, attr in ref.named_params():
+        assert rel_err(g.host(named[name].detach()), getattr(layer, attr)) < TOL, name
+
+
+def test_bn_relu_pool_block_golden_and_argmax():
+    import gpu_util as g
+    from mytorch_b200.backends.cuda.ops import max_pool2d_argmax
+    from mytorch_b200.examples.models import bn_relu_pool
+
+    gd = load_golden("models")
+    rng = np.random.default_rng(1002)
+    x = (0.5 + 2.0 * rng.standard_normal((8, 16, 12, 12))).astype(np.float32)
+    dy = rng.standard_normal((8, 16, 6, 6)).astype(np.float32)
+    net = bn_relu_pool(16)
+    net.to(g.DEV)
+    xt = g.dev(x, True)
+    y = net(xt)
+    (y * g.dev(dy)).sum().backward()
+    bn = net._modules["0"]
+    assert rel_err(g.host(y.detach()), gd["block/y"]) < 1e-5
+    assert rel_err(g.host(xt.grad), gd["block/dx"]) < 2e-5
+    assert rel_err(g.host(bn.weight.grad), gd["block/dgamma"]) < 2e-5 and rel_err(g.host(bn.bias.grad), gd["block/dbeta"]) < 2e-5
+    assert rel_err(g.host(bn.running_mean), gd["block/rm"]) < 1e-5 and rel_err(g.host(bn.running_var), gd["block/rv"]) < 1e-5
+    ref = OM.bn_relu_pool_block(x, dy, 16)
+    am = max_pool2d_argmax(y)
+    # ties only occur inside all-zero windows after ReLU; elsewhere the argmax must agree bit-exactly
+    nz = ref["y"] > 0
+    assert np.array_equal(am[nz], ref["argmax"].astype(np.uint8)[nz])
+
+
+def test_bn_relu_pool_block_benchmark_shape_reduced_batch():
+    """The benchmark block (128 channels, 56x56) at batch 16 against the oracle."""
+    import gpu_util as g
+    from mytorch_b200.examples.models import bn_relu_pool
+
+    rng = np.random.default_rng(1002)
+    x = (0.5 + 2.0 * rng.standard_normal((16, 128, 56, 56))).astype(np.float32)
+    dy = rng.standard_normal((16, 128, 28, 28)).astype(np.float32)
+    ref = OM.bn_relu_pool_block(x, dy, 128)
+    net = bn_relu_pool(128)
+    net.to(g.DEV)
+    xt = g.dev(x, True)
+    y = net(xt)
+    (y * g.dev(dy)).sum().backward()
+    bn = net._modules["0"]
+    assert rel_err(g.host(y.detach()), ref["y"]) < 1e-5
+    assert rel_err(g.host(xt.grad), ref["dx"]) < 2e-5
+    assert rel_err(g.host(bn.weight.grad), ref["dgamma"]) < 3e-5 and rel_err(g.host(bn.bias.grad), ref["dbeta"]) < 3e-5
+
+
+def test_step_is_bitwise_reproducible_and_graph_replay_matches_eager():
+    import gpu_util as g
+    import mytorch_b200 as mt
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.cuda_graph import StepGraph
+    from mytorch_b200.examples.models import ResNet18Cifar
+    from mytorch_b200.optim import SGD
+
+    rng = np.random.default_rng(9)
+    x = rng.standard_normal((16, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, 16).astype(np.int64)
+
+    def run(use_graph):
+        mt.manual_seed(21)
+        net = ResNet18Cifar((16, 16, 32, 32))
+        net.to(g.DEV)
+        opt = SGD(net.parameters(), lr=0.05, momentum=0.9)
+        xt, tt = g.dev(x), g.dev(t)
+
+        def step():
+            loss = F.cross_entropy(net(xt), tt)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+
+        losses = [step().item(), step().item()]
+        if use_graph:
+            sg = StepGraph(step, [xt, tt])
+            sg.capture()                      # capture executes nothing; it records step 3
+            for _ in range(2):
+                losses.append(sg.replay([x, t]).item())
+        else:
+            losses += [step().item(), step().item()]
+        return losses, [g.host(p.detach()) for p in net.parameters()]
+
+    l1, p1 = run(False)
+    l2, p2 = run(False)
+    l3, p3 = run(True)
+    assert l1 == l2 and all(np.array_equal(a, b) for a, b in zip(p1, p2))
+    assert l1 == l3 and all(np.array_equal(a, b) for a, b in zip(p1, p3))
