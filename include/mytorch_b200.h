@@ -29,6 +29,10 @@ enum MtbStatus { MTB_OK = 0, MTB_ERR_INVALID = 1, MTB_ERR_CUDA = 2, MTB_ERR_UNSU
 const char* mtb_last_error(void);
 int mtb_version(void);
 int mtb_device_check(void); /* MTB_OK iff the current device is compute capability 10.x */
+/* Synchronises the device and reports (then clears) the status word of the tensor-core kernels:
+ * 0 = fine, otherwise a bounded in-kernel wait ran out and that kernel exited without finishing.
+ * No counterpart in the reference (its kernels have no waits). status_out is a HOST pointer. */
+int mtb_tc_status(int* status_out);
 
 /* ---- convolution (replaces ConvForwardImplicitGEMM_float32 / ConvBackwardImplicitGEMM_float32,
  *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from

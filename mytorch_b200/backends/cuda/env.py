@@ -59,6 +59,7 @@ _SIGNATURES = {
     "mtb_conv2d_dgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_wgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_gemm_f32": ([_I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _P], _I),
+    "mtb_tc_status": ([_P], _I),
 }
 
 LIBRARY_PATH = os.environ.get(
@@ -126,6 +127,13 @@ class CudaEnv:
 
     def stream(self):
         return self.torch.cuda.current_stream().cuda_stream
+
+    def tensor_core_status(self):
+        """Synchronises and returns the status word of the tensor-core kernels (0 = fine; non-zero
+        = a bounded wait inside a kernel ran out and the kernel gave up).  Reading clears it."""
+        out = ctypes.c_int(0)
+        self.lib.tc_status(ctypes.byref(out))
+        return out.value
 
     def set_device(self, index):
         if index is not None and index != self.torch.cuda.current_device():

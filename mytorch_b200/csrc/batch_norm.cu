@@ -84,28 +84,41 @@ __global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __re
   }
 }
 
-// One thread per channel merges the P partials in order (double precision, tiny), writes the
-// batch mean / biased variance, the per-channel scale gamma/sqrt(var+eps) used by the
-// normalise pass, and blends the running statistics.
-__global__ void bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
-                                      float one_minus_m, float m, float* running_mean, float* running_var,
-                                      float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel: lane l merges partials l, l+32, ... in order, then the 32 lane results
+// are merged by a fixed shuffle tree (Chan's parallel update), so the result does not depend
+// on scheduling.  Writes the batch mean / biased variance, the per-channel scale
+// gamma/sqrt(var+eps) used by the normalise pass, and blends the running statistics.
+__device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, float nb, float mb, float qb) {
+  if (nb == 0.f) return;
+  float nt = n + nb;
+  float d = mb - mean;
+  float wb = nb / nt;
+  mean += d * wb;
+  m2 += qb + d * d * n * wb;
+  n = nt;
+}
+
+__global__ void __launch_bounds__(256) bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
+                                                              float one_minus_m, float m, float* running_mean, float* running_var,
+                                                              float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
+  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
   if (c >= C) return;
-  double n = 0, mean = 0, m2 = 0;
-  for (int p = 0; p < P; ++p) {
-    double nb = partial[(long long)p * 3 * C + c];
-    if (nb == 0) continue;
-    double mb = partial[(long long)p * 3 * C + C + c];
-    double qb = partial[(long long)p * 3 * C + 2 * C + c];
-    double nt = n + nb;
-    double d = mb - mean;
-    mean += d * nb / nt;
-    m2 += qb + d * d * n * nb / nt;
-    n = nt;
+  float n = 0.f, mean = 0.f, m2 = 0.f;
+  for (int p = lane; p < P; p += 32) {
+    const float* q = partial + (long long)p * 3 * C + c;
+    chan_merge(n, mean, m2, q[0], q[C], q[2 * C]);
   }
-  float mu = (float)mean;
-  float var = n > 0 ? (float)(m2 / n) : 0.f;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    float nb = __shfl_down_sync(0xffffffffu, n, o);
+    float mb = __shfl_down_sync(0xffffffffu, mean, o);
+    float qb = __shfl_down_sync(0xffffffffu, m2, o);
+    chan_merge(n, mean, m2, nb, mb, qb);
+  }
+  if (lane != 0) return;
+  float mu = mean;
+  float var = n > 0.f ? m2 / n : 0.f;
   mean_out[c] = mu;
   var_out[c] = var;
   float rstd = 1.0f / sqrtf(var + eps);
@@ -209,17 +222,25 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
 }
 
 // dbeta = sum dy, dgamma = sum dy*xhat; coefficients for dx = k1 * (dy - k2 - (x - mean) * k3).
-__global__ void bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
-                                    const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
-                                    float* __restrict__ dbeta, float* __restrict__ coef) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel, fixed summation order.
+__global__ void __launch_bounds__(256) bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
+                                                            const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
+                                                            float* __restrict__ dbeta, float* __restrict__ coef) {
+  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
   if (c >= C) return;
-  double s0 = 0, s1 = 0;
-  for (int p = 0; p < P; ++p) {
+  float s0 = 0.f, s1 = 0.f;
+  for (int p = lane; p < P; p += 32) {
     s0 += partial[(long long)p * 2 * C + c];
     s1 += partial[(long long)p * 2 * C + C + c];
   }
-  float db = (float)s0, dg = (float)s1;
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    s0 += __shfl_down_sync(0xffffffffu, s0, o);
+    s1 += __shfl_down_sync(0xffffffffu, s1, o);
+  }
+  if (lane != 0) return;
+  float db = s0, dg = s1;
   if (dbeta) dbeta[c] = db;
   if (dgamma) dgamma[c] = dg;
   float rstd = 1.0f / sqrtf(var[c] + eps);
@@ -305,7 +326,7 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
     if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
-    bn_stats_final_kernel<<<fin_blocks, 128, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+    bn_stats_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
                                                       running_mean, running_var, mean, var, scale);
     MTB_LAUNCH_CHECK("bn_stats_final_kernel");
   } else {
@@ -341,7 +362,7 @@ MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const floa
   if (cfg.vec == 4) bn_bwd_partial_kernel<4><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
   else bn_bwd_partial_kernel<1><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
   MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
-  bn_bwd_final_kernel<<<mtb_div_up(c, 128), 128, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+  bn_bwd_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
                                                           dgamma, dbeta, coef);
   MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
   ColCfg s = stream_cfg(rows, c, aligned);

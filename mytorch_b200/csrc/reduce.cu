@@ -41,12 +41,16 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const float* __rest
   }
 }
 
-__global__ void colsum_final_kernel(const float* __restrict__ partial, int P, int C, float scale, float* __restrict__ out) {
-  int c = blockIdx.x * blockDim.x + threadIdx.x;
+// One warp per channel, fixed summation order.
+__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int P, int C, float scale, float* __restrict__ out) {
+  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
+  int lane = threadIdx.x & 31;
   if (c >= C) return;
-  double s = 0;
-  for (int p = 0; p < P; ++p) s += partial[(long long)p * C + c];
-  out[c] = (float)s * scale;
+  float s = 0.f;
+  for (int p = lane; p < P; p += 32) s += partial[(long long)p * C + c];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
+  if (lane == 0) out[c] = s * scale;
 }
 
 // y[n, c] = scale * sum_{hw} x[n, hw, c]; one thread per (n, c) with c fastest (coalesced).
@@ -121,7 +125,7 @@ MTB_API int mtb_colsum_f32(const float* a, long long rows, int c, float scale, f
   if (cfg.vec == 4) colsum_partial_kernel<4><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   else colsum_partial_kernel<1><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   MTB_LAUNCH_CHECK("colsum_partial_kernel");
-  colsum_final_kernel<<<mtb_div_up(c, 128), 128, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
+  colsum_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
   MTB_LAUNCH_CHECK("colsum_final_kernel");
   return MTB_OK;
 }

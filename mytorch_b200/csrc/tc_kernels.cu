@@ -1,0 +1,437 @@
+// tcgen05 / TMEM / TMA kernels: TF32 GEMM with FP32 accumulation for Linear layers, and
+// implicit-GEMM convolution forward and (stride-1) data gradient over channels-last tensors.
+//
+// One persistent CTA per SM, 192 threads in three roles:
+//   warp 0     TMA producer: one lane fills a ring of shared-memory stages (A tile 128 x 32,
+//              B tile BN x 32 fp32, 128-byte swizzle).  The convolution's A operand is never
+//              materialised: an im2col-mode tensor map gathers 128 output pixels x 32 channels
+//              of one filter tap per load, with zero fill for the padding halo.
+//   warp 1     MMA issuer: one lane issues tcgen05.mma kind::tf32 (128 x BN x 8 per instruction),
+//              accumulating in TMEM; tcgen05.commit releases stages and publishes finished tiles.
+//   warps 2-5  epilogue: tcgen05.ld the accumulator (each warp owns a 32-lane TMEM quarter),
+//              add bias / apply ReLU, store rows to global memory.
+// Two TMEM accumulator buffers let the epilogue of tile i overlap the main loop of tile i+1.
+// All waits are bounded (tc_common.cuh); a kernel that gives up sets g_tc_status and exits.
+#include "tc_common.cuh"
+#include "kernels.h"
+#include <cudaTypedefs.h>
+
+namespace tc {
+
+static PFN_cuTensorMapEncodeTiled_v12000 g_encode_tiled = nullptr;
+static PFN_cuTensorMapEncodeIm2col_v12000 g_encode_im2col = nullptr;
+
+// Element type recorded in the tensor maps.  FLOAT32 hands the bits to the MMA unchanged (the
+// tensor core then ignores the low 13 mantissa bits); MTB_TMA_TFLOAT32=1 selects the TFLOAT32
+// type for experiments.
+static CUtensorMapDataType tma_dtype() {
+  static int mode = -1;
+  if (mode < 0) mode = getenv("MTB_TMA_TFLOAT32") ? 1 : 0;
+  return mode ? CU_TENSOR_MAP_DATA_TYPE_TFLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+}
+
+static int load_driver_entry_points() {
+  if (g_encode_tiled && g_encode_im2col) return MTB_OK;
+  cudaDriverEntryPointQueryResult q;
+  void* fn = nullptr;
+  MTB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+  if (q != cudaDriverEntryPointSuccess || !fn) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeTiled is not available in this driver");
+  g_encode_tiled = (PFN_cuTensorMapEncodeTiled_v12000)fn;
+  fn = nullptr;
+  MTB_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q));
+  if (q != cudaDriverEntryPointSuccess || !fn) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeIm2col is not available in this driver");
+  g_encode_im2col = (PFN_cuTensorMapEncodeIm2col_v12000)fn;
+  return MTB_OK;
+}
+
+int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows) {
+  int rc = load_driver_entry_points();
+  if (rc) return rc;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch_elems * 4};
+  cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = g_encode_tiled(map, tma_dtype(), 2, const_cast<float*>(base), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld pitch=%lld box=%dx%d", (int)r, rows, cols, pitch_elems, box_cols, box_rows);
+  return MTB_OK;
+}
+
+int encode_im2col_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int lower_w, int lower_h, int upper_w, int upper_h,
+                     int stride_w, int stride_h, int channels, int pixels) {
+  int rc = load_driver_entry_points();
+  if (rc) return rc;
+  cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)c * 4, (cuuint64_t)w * c * 4, (cuuint64_t)h * w * c * 4};
+  int lower[2] = {lower_w, lower_h};
+  int upper[2] = {upper_w, upper_h};
+  cuuint32_t estr[4] = {1, (cuuint32_t)stride_w, (cuuint32_t)stride_h, 1};
+  CUresult r = g_encode_im2col(map, tma_dtype(), 4, const_cast<float*>(base), dims, strides, lower, upper,
+                               (cuuint32_t)channels, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d) n=%d h=%d w=%d c=%d lower=(%d,%d) upper=(%d,%d) stride=(%d,%d)", (int)r, n,
+                    h, w, c, lower_w, lower_h, upper_w, upper_h, stride_w, stride_h);
+  return MTB_OK;
+}
+
+}  // namespace tc
+
+namespace {
+using namespace tc;
+
+enum { A_KMAJOR = 0, A_MNMAJOR = 1, A_IM2COL = 2 };
+enum { B_KMAJOR = 0, B_MNMAJOR = 1 };
+
+struct GemmParams {
+  int M, N;
+  int num_kb;  // reduction blocks of 32
+  int m_tiles, n_tiles;
+  float* out;
+  long long ldo;
+  const float* bias;
+  int relu;
+  // geometry of the im2col'ed tensor (A operand of a convolution)
+  int OW, OH, SW, SH, PW, PH, KW, KH, cchunks;
+  // B operand addressed per filter tap (data gradient: weights read in place, taps reversed)
+  int b_per_tap;      // 0: B inner coordinate is n0 (+32j), outer kb*32.  1: see producer
+  int b_tap_elems;    // elements between consecutive taps along B's inner dimension
+};
+
+template <int BN>
+struct Cfg {
+  static constexpr int kStages = BN == 256 ? 4 : 6;
+  static constexpr uint32_t kABytes = 128 * 32 * 4;
+  static constexpr uint32_t kBBytes = BN * 32 * 4;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
+  static constexpr uint32_t kTmemCols = 2 * BN;
+};
+
+template <int BN, int AMODE, int BMODE>
+__global__ void __launch_bounds__(192, 1)
+tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmParams p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[8], bar_empty[8], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tfull[b]), 1);
+      mbar_init(smem_u32(&bar_tempty[b]), 128);
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int tiles = p.m_tiles * p.n_tiles;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&mapA);
+      prefetch_tensormap(&mapB);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
+        int pix_w = 0, pix_h = 0, pix_n = 0;
+        if (AMODE == A_IM2COL) {
+          int ow = m0 % p.OW, t = m0 / p.OW;
+          pix_w = ow * p.SW - p.PW;
+          pix_h = (t % p.OH) * p.SH - p.PH;
+          pix_n = t / p.OH;
+        }
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 1)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          mbar_expect_tx(full, C::kStageBytes);
+          const uint32_t a_dst = smem_base + stage * C::kStageBytes, b_dst = a_dst + C::kABytes;
+          int tap = 0, cc = kb;
+          if (AMODE == A_IM2COL) { tap = kb / p.cchunks; cc = kb - tap * p.cchunks; }
+          if (AMODE == A_KMAJOR) {
+            tma_load_2d(a_dst, &mapA, full, kb * 32, m0);
+          } else if (AMODE == A_MNMAJOR) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) tma_load_2d(a_dst + j * 4096, &mapA, full, m0 + 32 * j, kb * 32);
+          } else {
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            tma_load_im2col_4d(a_dst, &mapA, full, cc * 32, pix_w, pix_h, pix_n, (uint16_t)kw, (uint16_t)kh);
+          }
+          if (BMODE == B_KMAJOR) {
+            tma_load_2d(b_dst, &mapB, full, kb * 32, n0);
+          } else {
+            int bx = n0, by = kb * 32;
+            if (p.b_per_tap) { bx = (p.KH * p.KW - 1 - tap) * p.b_tap_elems + n0; by = cc * 32; }
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, full, bx + 32 * j, by);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(128, BN, AMODE == A_MNMAJOR ? 1 : 0, BMODE == B_MNMAJOR ? 1 : 0);
+      int stage = 0;
+      uint32_t phase = 0;
+      int t = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+        const int buf = t & 1;
+        const uint32_t use = (uint32_t)(t >> 1);
+        if (!mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 2)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 3)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::kStageBytes, b_addr = a_addr + C::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            const uint64_t ad = AMODE == A_MNMAJOR ? smem_desc_sw128(a_addr + kk * 1024, 4096, 1024) : smem_desc_sw128(a_addr + kk * 32, 16, 1024);
+            const uint64_t bd = BMODE == B_MNMAJOR ? smem_desc_sw128(b_addr + kk * 1024, 4096, 1024) : smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+            mma_tf32(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&bar_empty[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit(smem_u32(&bar_tfull[buf]));
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    int t = 0;
+    const bool vec_ok = (p.ldo % 4 == 0) && (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias)) & 15u) == 0);
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
+      const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      bool ok = mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 4);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m0 + quarter * 32 + lane;
+      float* orow = p.out + (long long)row * p.ldo;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < p.M && col0 < p.N) {
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+              }
+              if (p.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+              *reinterpret_cast<float4*>(orow + col0 + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.N) {
+                float v = __uint_as_float(r[j]);
+                if (p.bias) v += p.bias[col0 + j];
+                if (p.relu) v = fmaxf(v, 0.f);
+                orow[col0 + j] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_tempty[buf]));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    // give copies that are still in flight time to land before the CTA's shared memory is released
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+template <int BN, int AMODE, int BMODE>
+int launch_tc(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t st) {
+  using C = Cfg<BN>;
+  auto kernel = tc_gemm_kernel<BN, AMODE, BMODE>;
+  static bool configured = false;
+  if (!configured) {
+    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
+    configured = true;
+  }
+  int tiles = p.m_tiles * p.n_tiles;
+  int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
+  kernel<<<grid, 192, C::kSmemBytes, st>>>(mapA, mapB, p);
+  MTB_LAUNCH_CHECK("tc_gemm_kernel");
+  return MTB_OK;
+}
+
+template <int AMODE, int BMODE>
+int launch_tc_bn(int bn, const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t st) {
+  if (bn == 64) return launch_tc<64, AMODE, BMODE>(mapA, mapB, p, st);
+  if (bn == 128) return launch_tc<128, AMODE, BMODE>(mapA, mapB, p, st);
+  return launch_tc<256, AMODE, BMODE>(mapA, mapB, p, st);
+}
+
+int pick_bn(int n) { return n <= 64 ? 64 : (n <= 128 ? 128 : 256); }
+
+bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Activations smaller than this stay on the CUDA-core kernels: tiny tensors gain nothing from
+// the tensor cores, and im2col tensor maps over very small tensors are avoided altogether.
+constexpr long long kMinIm2colBytes = 256 * 1024;
+
+}  // namespace
+
+// ------------------------------------------------------------------------------ host API
+
+// Reads (and clears) the status word the tensor-core kernels set when a bounded wait ran out.
+// Synchronises the device.
+MTB_API int mtb_tc_status(int* status_out) {
+  int h[8] = {0};
+  MTB_CUDA(cudaDeviceSynchronize());
+  MTB_CUDA(cudaMemcpyFromSymbol(h, g_tc_status, sizeof(h)));
+  if (status_out) *status_out = h[0];
+  if (h[0] != 0) {
+    int z[8] = {0};
+    MTB_CUDA(cudaMemcpyToSymbol(g_tc_status, z, sizeof(z)));
+  }
+  return MTB_OK;
+}
+
+bool mtb_tc_gemm_supported(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* c) {
+  if (getenv("MTB_DISABLE_TC")) return false;
+  if (!al16(a) || !al16(b) || !al16(c)) return false;
+  if (m < 32 || n < 8 || k < 32) return false;
+  if (k % 4) return false;                 // K-major pitches
+  if (trans_a && m % 4) return false;      // A stored [K][M]
+  if (!trans_b && n % 4) return false;     // B stored [K][N]
+  return true;
+}
+
+int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu, float* c,
+                    void* stream) {
+  CUtensorMap mapA, mapB;
+  int bn = pick_bn(n);
+  int rc;
+  if (!trans_a) rc = tc::encode_tiled_2d(&mapA, a, m, k, k, 32, 128);
+  else rc = tc::encode_tiled_2d(&mapA, a, k, m, m, 32, 32);
+  if (rc) return rc;
+  if (trans_b) rc = tc::encode_tiled_2d(&mapB, b, n, k, k, 32, bn);
+  else rc = tc::encode_tiled_2d(&mapB, b, k, n, n, 32, 32);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = m; p.N = n; p.num_kb = (k + 31) / 32;
+  p.m_tiles = (m + 127) / 128; p.n_tiles = (n + bn - 1) / bn;
+  p.out = c; p.ldo = n; p.bias = bias; p.relu = relu;
+  cudaStream_t st = (cudaStream_t)stream;
+  if (!trans_a && trans_b) return launch_tc_bn<A_KMAJOR, B_KMAJOR>(bn, mapA, mapB, p, st);
+  if (!trans_a && !trans_b) return launch_tc_bn<A_KMAJOR, B_MNMAJOR>(bn, mapA, mapB, p, st);
+  if (trans_a && trans_b) return launch_tc_bn<A_MNMAJOR, B_KMAJOR>(bn, mapA, mapB, p, st);
+  return launch_tc_bn<A_MNMAJOR, B_MNMAJOR>(bn, mapA, mapB, p, st);
+}
+
+long long mtb_tc_conv2d_workspace_bytes(int, int, int, int, int, int, int, int, int, int, int) { return 0; }
+
+bool mtb_tc_conv2d_forward_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                     const float* wt, const float* y) {
+  if (getenv("MTB_DISABLE_TC")) return false;
+  if (!al16(x) || !al16(wt) || !al16(y)) return false;
+  if (cin % 32 || cout % 4) return false;
+  if (sh > 8 || sw > 8 || ph > 100 || pw > 100 || kh > 32 || kw > 32) return false;
+  if ((long long)n * h * w * cin * 4 < kMinIm2colBytes) return false;
+  return true;
+}
+
+int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                              const float* wt, const float* bias, float* y, int relu, void* stream) {
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  const long long M = (long long)n * oh * ow, K = (long long)kh * kw * cin;
+  const int bn = pick_bn(cout);
+  CUtensorMap mapA, mapB;
+  int rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
+  if (rc) return rc;
+  rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = (int)M; p.N = cout; p.num_kb = (int)(K / 32);
+  p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cout + bn - 1) / bn;
+  p.out = y; p.ldo = cout; p.bias = bias; p.relu = relu;
+  p.OW = ow; p.OH = oh; p.SW = sw; p.SH = sh; p.PW = pw; p.PH = ph; p.KW = kw; p.KH = kh; p.cchunks = cin / 32;
+  return launch_tc_bn<A_IM2COL, B_KMAJOR>(bn, mapA, mapB, p, (cudaStream_t)stream);
+}
+
+bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                                   const float* wt, const float* dx) {
+  if (getenv("MTB_DISABLE_TC")) return false;
+  if (!al16(dy) || !al16(wt) || !al16(dx)) return false;
+  if (sh != 1 || sw != 1) return false;            // strided layers use the gather kernel
+  if (cout % 32 || cin % 4) return false;
+  if (ph > kh - 1 || pw > kw - 1 || kh > 32 || kw > 32) return false;
+  const int oh = h + 2 * ph - kh + 1, ow = w + 2 * pw - kw + 1;
+  if ((long long)n * oh * ow * cout * 4 < kMinIm2colBytes) return false;
+  return true;
+}
+
+// dX = conv(dY, W rotated by 180 degrees) with padding K-1-p.  dY plays the activation role of
+// the forward kernel; W is read in place as an MN-major operand (for one tap, rows are output
+// channels = the reduction index, columns are input channels), taps visited in reverse.
+int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                            const float* wt, float* dx, void*, long long, void* stream) {
+  const int oh = h + 2 * ph - kh + 1, ow = w + 2 * pw - kw + 1;
+  const int qh = kh - 1 - ph, qw = kw - 1 - pw;  // padding of the transposed problem
+  const long long M = (long long)n * h * w;
+  const int bn = pick_bn(cin);
+  CUtensorMap mapA, mapB;
+  int rc = tc::encode_im2col_4d(&mapA, dy, n, oh, ow, cout, -qw, -qh, qw - (kw - 1), qh - (kh - 1), 1, 1, 32, 128);
+  if (rc) return rc;
+  rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32);
+  if (rc) return rc;
+  GemmParams p{};
+  p.M = (int)M; p.N = cin; p.num_kb = kh * kw * (cout / 32);
+  p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
+  p.out = dx; p.ldo = cin; p.bias = nullptr; p.relu = 0;
+  p.OW = w; p.OH = h; p.SW = 1; p.SH = 1; p.PW = qw; p.PH = qh; p.KW = kw; p.KH = kh; p.cchunks = cout / 32;
+  p.b_per_tap = 1; p.b_tap_elems = cin;
+  return launch_tc_bn<A_IM2COL, B_MNMAJOR>(bn, mapA, mapB, p, (cudaStream_t)stream);
+}
+
+bool mtb_tc_conv2d_wgrad_supported(int, int, int, int, int, int, int, int, int, int, int, const float*, const float*, const float*) { return false; }
+int mtb_tc_conv2d_wgrad_f32(int, int, int, int, int, int, int, int, int, int, int, const float*, const float*, float*, void*, long long, void*) {
+  return mtb_fail(MTB_ERR_UNSUPPORTED, "tensor-core conv wgrad not built");
+}

@@ -26,6 +26,17 @@ def rel_err(a, b):
     return float(np.max(np.abs(a - b)) / max(float(np.max(np.abs(b))), 1e-30))
 
 
+def rel_l2(a, b):
+    """||a-b||_2 / ||b||_2 — used for whole-model gradients.  A pre-activation that is within
+    rounding distance of 0 can fall on different sides of a ReLU in two correct implementations;
+    the gradient at that one element then differs by its full magnitude, so a max-norm comparison
+    of activation or weight gradients through many ReLU layers is ill-conditioned while the L2
+    error stays of the order sqrt(fraction of flipped elements)."""
+    a = np.asarray(a, dtype=np.float64).reshape(-1)
+    b = np.asarray(b, dtype=np.float64).reshape(-1)
+    return float(np.linalg.norm(a - b) / max(float(np.linalg.norm(b)), 1e-30))
+
+
 def summarize(arr, sample=64):
     a = np.asarray(arr, dtype=np.float64).reshape(-1)
     idx = np.linspace(0, a.size - 1, min(sample, a.size)).astype(np.int64)
