@@ -130,17 +130,30 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Shared-memory matrix descriptor, 128-byte swizzle.  K-major operand: rows of 128 B (32 fp32 of
-// K), 8-row groups `sbo` bytes apart (1024 when packed), lbo unused (encoded as 16 B).
-// MN-major operand: 128-byte rows hold 32 consecutive M/N elements for one k; 8 such rows form
-// one K group; `lbo` = bytes between 32-wide M/N blocks, `sbo` = bytes between K groups.
-__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+// Shared-memory matrix descriptors.
+// K-major operand (SWIZZLE_128B, TMA swizzle 128B): rows of 128 B hold 32 fp32 of K for one
+// M/N index; 16-byte chunks are XOR-swizzled by (row % 8); 8-row groups are `sbo` bytes apart
+// (1024 when packed); lbo is unused (encoded as 16 B).
+__device__ __forceinline__ uint64_t smem_desc_kmajor(uint32_t saddr, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
+  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  return d;
+}
+// MN-major operand of a 32-bit type (the only layout tcgen05 accepts for it: 128-byte swizzle
+// with a 32-byte atom base; TMA swizzle 128B_ATOM_32B): rows of 128 B hold 32 consecutive M/N
+// elements for one k; 32-byte chunks are XOR-swizzled by (row % 4); 4 rows form one K group;
+// `lbo` = bytes between 32-wide M/N blocks, `sbo` = bytes between K groups (512 when packed).
+__device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
   uint64_t d = 0;
   d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
   d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
   d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
-  d |= (uint64_t)1 << 46;  // descriptor version for sm_100
-  d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)1 << 61;  // SWIZZLE_128B_BASE32B
   return d;
 }
 
@@ -153,11 +166,13 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, int a_mn_major, 
 // ---- host: tensor maps ----
 // fp32 matrix [rows][cols] row-major (row pitch `pitch_elems`), boxes of box_cols x box_rows
 // elements, 128-byte swizzle, zero fill outside the matrix.
-int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows);
+// mn_major selects the 32-byte-atom swizzle that MN-major tcgen05 operands need.
+int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows,
+                    bool mn_major = false);
 // channels-last activation {C, W, H, N}; a load takes `pixels` output pixels x `channels`
 // channels for one filter tap of a convolution with the given stride / lower padding; `upper`
 // = lower_pad - (filter - 1) per spatial dim bounds the walk of the window origin.
 int encode_im2col_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int lower_w, int lower_h, int upper_w, int upper_h,
-                     int stride_w, int stride_h, int channels, int pixels);
+                     int stride_w, int stride_h, int channels, int pixels, bool mn_major = false);
 
 }  // namespace tc

@@ -44,7 +44,8 @@ static int load_driver_entry_points() {
   return MTB_OK;
 }
 
-int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows) {
+int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows,
+                    bool mn_major) {
   int rc = load_driver_entry_points();
   if (rc) return rc;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
@@ -52,14 +53,14 @@ int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long lo
   cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = g_encode_tiled(map, tma_dtype(), 2, const_cast<float*>(base), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B,
+                              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeTiled failed (%d) rows=%lld cols=%lld pitch=%lld box=%dx%d", (int)r, rows, cols, pitch_elems, box_cols, box_rows);
   return MTB_OK;
 }
 
 int encode_im2col_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int lower_w, int lower_h, int upper_w, int upper_h,
-                     int stride_w, int stride_h, int channels, int pixels) {
+                     int stride_w, int stride_h, int channels, int pixels, bool mn_major) {
   int rc = load_driver_entry_points();
   if (rc) return rc;
   cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
@@ -68,8 +69,9 @@ int encode_im2col_4d(CUtensorMap* map, const float* base, int n, int h, int w, i
   int upper[2] = {upper_w, upper_h};
   cuuint32_t estr[4] = {1, (cuuint32_t)stride_w, (cuuint32_t)stride_h, 1};
   CUresult r = g_encode_im2col(map, tma_dtype(), 4, const_cast<float*>(base), dims, strides, lower, upper,
-                               (cuuint32_t)channels, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                               (cuuint32_t)channels, (cuuint32_t)pixels, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                               mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeIm2col failed (%d) n=%d h=%d w=%d c=%d lower=(%d,%d) upper=(%d,%d) stride=(%d,%d)", (int)r, n,
                     h, w, c, lower_w, lower_h, upper_w, upper_h, stride_w, stride_h);
@@ -94,9 +96,13 @@ struct GemmParams {
   int relu;
   // geometry of the im2col'ed tensor (A operand of a convolution)
   int OW, OH, SW, SH, PW, PH, KW, KH, cchunks;
-  // B operand addressed per filter tap (data gradient: weights read in place, taps reversed)
-  int b_per_tap;      // 0: B inner coordinate is n0 (+32j), outer kb*32.  1: see producer
-  int b_tap_elems;    // elements between consecutive taps along B's inner dimension
+  // B operand addressed per filter tap (data gradient: weights read in place).  When set, the
+  // k-block (tap, cc) reads B at inner coordinate b_tap_x[tap] + n0 (+32j), outer cc*32.
+  int b_per_tap;
+  int b_tap_x[64];
+  // Output rows are pixels of a strided sub-grid of an [N, o_H, o_W, ldo] tensor: row
+  // (n, i, j) of an o_Hc x o_Wc grid lands on pixel (o_h0 + o_sh*i, o_w0 + o_sw*j).
+  int o_strided, o_Hc, o_Wc, o_H, o_W, o_h0, o_w0, o_sh, o_sw;
 };
 
 template <int BN>
@@ -183,7 +189,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             tma_load_2d(b_dst, &mapB, full, kb * 32, n0);
           } else {
             int bx = n0, by = kb * 32;
-            if (p.b_per_tap) { bx = (p.KH * p.KW - 1 - tap) * p.b_tap_elems + n0; by = cc * 32; }
+            if (p.b_per_tap) { bx = p.b_tap_x[tap] + n0; by = cc * 32; }
 #pragma unroll
             for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, full, bx + 32 * j, by);
           }
@@ -211,8 +217,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           const uint32_t a_addr = smem_base + stage * C::kStageBytes, b_addr = a_addr + C::kABytes;
 #pragma unroll
           for (int kk = 0; kk < 4; ++kk) {
-            const uint64_t ad = AMODE == A_MNMAJOR ? smem_desc_sw128(a_addr + kk * 1024, 4096, 1024) : smem_desc_sw128(a_addr + kk * 32, 16, 1024);
-            const uint64_t bd = BMODE == B_MNMAJOR ? smem_desc_sw128(b_addr + kk * 1024, 4096, 1024) : smem_desc_sw128(b_addr + kk * 32, 16, 1024);
+            const uint64_t ad = AMODE == A_MNMAJOR ? smem_desc_mnmajor(a_addr + kk * 1024, 4096, 512) : smem_desc_kmajor(a_addr + kk * 32, 1024);
+            const uint64_t bd = BMODE == B_MNMAJOR ? smem_desc_mnmajor(b_addr + kk * 1024, 4096, 512) : smem_desc_kmajor(b_addr + kk * 32, 1024);
             mma_tf32(d_tmem, ad, bd, idesc, (kb | kk) != 0 ? 1u : 0u);
           }
           mma_commit(smem_u32(&bar_empty[stage]));
@@ -235,7 +241,13 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       if (!ok) break;
       tc_fence_after();
       const int row = m0 + quarter * 32 + lane;
-      float* orow = p.out + (long long)row * p.ldo;
+      long long orow_index = row;
+      if (p.o_strided && row < p.M) {
+        const int j = row % p.o_Wc, t2 = row / p.o_Wc;
+        const int i = t2 % p.o_Hc, nn = t2 / p.o_Hc;
+        orow_index = ((long long)nn * p.o_H + p.o_h0 + p.o_sh * i) * p.o_W + p.o_w0 + p.o_sw * j;
+      }
+      float* orow = p.out + orow_index * p.ldo;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -350,10 +362,10 @@ int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const floa
   int bn = pick_bn(n);
   int rc;
   if (!trans_a) rc = tc::encode_tiled_2d(&mapA, a, m, k, k, 32, 128);
-  else rc = tc::encode_tiled_2d(&mapA, a, k, m, m, 32, 32);
+  else rc = tc::encode_tiled_2d(&mapA, a, k, m, m, 32, 32, true);
   if (rc) return rc;
   if (trans_b) rc = tc::encode_tiled_2d(&mapB, b, n, k, k, 32, bn);
-  else rc = tc::encode_tiled_2d(&mapB, b, k, n, n, 32, 32);
+  else rc = tc::encode_tiled_2d(&mapB, b, k, n, n, 32, 32, true);
   if (rc) return rc;
   GemmParams p{};
   p.M = m; p.N = n; p.num_kb = (k + 31) / 32;
@@ -365,8 +377,6 @@ int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const floa
   if (trans_a && trans_b) return launch_tc_bn<A_MNMAJOR, B_KMAJOR>(bn, mapA, mapB, p, st);
   return launch_tc_bn<A_MNMAJOR, B_MNMAJOR>(bn, mapA, mapB, p, st);
 }
-
-long long mtb_tc_conv2d_workspace_bytes(int, int, int, int, int, int, int, int, int, int, int) { return 0; }
 
 bool mtb_tc_conv2d_forward_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                                      const float* wt, const float* y) {
@@ -400,38 +410,353 @@ bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw,
                                    const float* wt, const float* dx) {
   if (getenv("MTB_DISABLE_TC")) return false;
   if (!al16(dy) || !al16(wt) || !al16(dx)) return false;
-  if (sh != 1 || sw != 1) return false;            // strided layers use the gather kernel
   if (cout % 32 || cin % 4) return false;
-  if (ph > kh - 1 || pw > kw - 1 || kh > 32 || kw > 32) return false;
-  const int oh = h + 2 * ph - kh + 1, ow = w + 2 * pw - kw + 1;
+  if (kh * kw > 64 || sh > 8 || sw > 8 || ph > 64 || pw > 64) return false;
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   if ((long long)n * oh * ow * cout * 4 < kMinIm2colBytes) return false;
   return true;
 }
 
-// dX = conv(dY, W rotated by 180 degrees) with padding K-1-p.  dY plays the activation role of
-// the forward kernel; W is read in place as an MN-major operand (for one tap, rows are output
-// channels = the reduction index, columns are input channels), taps visited in reverse.
+// Data gradient.  For stride 1 this is a convolution of dY with the filter rotated by 180
+// degrees.  For stride s the input pixels fall into s*s residue classes; pixels of class (a, b)
+// only see the taps kh = a (mod s), kw = b (mod s), and over the class's own (coarser) grid
+// that is again a stride-1 convolution of dY with that sub-filter.  Each class is one launch of
+// the implicit-GEMM kernel: dY plays the activation role (im2col-mode loads with zero fill
+// beyond the edges), the weights are read in place as an MN-major operand (for one tap, rows
+// are output channels = the reduction index, columns are input channels), and the epilogue
+// scatters rows to the class's pixels.  Classes without taps (stride larger than the filter)
+// receive zeros.  No atomics; every element of dX is written exactly once.
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                             const float* wt, float* dx, void*, long long, void* stream) {
-  const int oh = h + 2 * ph - kh + 1, ow = w + 2 * pw - kw + 1;
-  const int qh = kh - 1 - ph, qw = kw - 1 - pw;  // padding of the transposed problem
-  const long long M = (long long)n * h * w;
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   const int bn = pick_bn(cin);
-  CUtensorMap mapA, mapB;
-  int rc = tc::encode_im2col_4d(&mapA, dy, n, oh, ow, cout, -qw, -qh, qw - (kw - 1), qh - (kh - 1), 1, 1, 32, 128);
+  cudaStream_t st = (cudaStream_t)stream;
+  CUtensorMap mapB;
+  int rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32, true);
   if (rc) return rc;
-  rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32);
-  if (rc) return rc;
-  GemmParams p{};
-  p.M = (int)M; p.N = cin; p.num_kb = kh * kw * (cout / 32);
-  p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
-  p.out = dx; p.ldo = cin; p.bias = nullptr; p.relu = 0;
-  p.OW = w; p.OH = h; p.SW = 1; p.SH = 1; p.PW = qw; p.PH = qh; p.KW = kw; p.KH = kh; p.cchunks = cout / 32;
-  p.b_per_tap = 1; p.b_tap_elems = cin;
-  return launch_tc_bn<A_IM2COL, B_MNMAJOR>(bn, mapA, mapB, p, (cudaStream_t)stream);
+  struct Axis { int taps, start, count, lower, upper; };
+  auto axis = [](int a, int size, int osize, int k, int s, int pad) {
+    Axis r{};
+    r.taps = a < k ? (k - a + s - 1) / s : 0;
+    r.start = (((a - pad) % s) + s) % s;
+    r.count = r.start < size ? (size - r.start + s - 1) / s : 0;
+    const int c0 = (r.start + pad - a) / s;
+    r.lower = c0 - (r.taps - 1);
+    r.upper = r.count - osize + r.lower;
+    return r;
+  };
+  bool need_zero = false;
+  for (int a = 0; a < sh; ++a)
+    for (int b = 0; b < sw; ++b) {
+      Axis ah = axis(a, h, oh, kh, sh, ph), aw = axis(b, w, ow, kw, sw, pw);
+      if (ah.count > 0 && aw.count > 0 && (ah.taps == 0 || aw.taps == 0)) need_zero = true;
+    }
+  if (need_zero) MTB_CUDA(cudaMemsetAsync(dx, 0, (size_t)n * h * w * cin * 4, st));
+  for (int a = 0; a < sh; ++a) {
+    for (int b = 0; b < sw; ++b) {
+      Axis ah = axis(a, h, oh, kh, sh, ph), aw = axis(b, w, ow, kw, sw, pw);
+      if (ah.count == 0 || aw.count == 0 || ah.taps == 0 || aw.taps == 0) continue;
+      CUtensorMap mapA;
+      rc = tc::encode_im2col_4d(&mapA, dy, n, oh, ow, cout, aw.lower, ah.lower, aw.upper, ah.upper, 1, 1, 32, 128);
+      if (rc) return rc;
+      GemmParams p{};
+      const long long M = (long long)n * ah.count * aw.count;
+      p.M = (int)M; p.N = cin; p.num_kb = ah.taps * aw.taps * (cout / 32);
+      p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
+      p.out = dx; p.ldo = cin; p.bias = nullptr; p.relu = 0;
+      p.OW = aw.count; p.OH = ah.count; p.SW = 1; p.SH = 1; p.PW = -aw.lower; p.PH = -ah.lower; p.KW = aw.taps; p.KH = ah.taps;
+      p.cchunks = cout / 32;
+      p.b_per_tap = 1;
+      for (int jh = 0; jh < ah.taps; ++jh)
+        for (int jw = 0; jw < aw.taps; ++jw) {
+          const int fkh = a + sh * (ah.taps - 1 - jh), fkw = b + sw * (aw.taps - 1 - jw);  // dY offset j <-> filter tap
+          p.b_tap_x[jh * aw.taps + jw] = (fkh * kw + fkw) * cin;
+        }
+      p.o_strided = 1; p.o_Hc = ah.count; p.o_Wc = aw.count; p.o_H = h; p.o_W = w; p.o_h0 = ah.start; p.o_w0 = aw.start; p.o_sh = sh; p.o_sw = sw;
+      rc = launch_tc_bn<A_IM2COL, B_MNMAJOR>(bn, mapA, mapB, p, st);
+      if (rc) return rc;
+    }
+  }
+  return MTB_OK;
 }
 
-bool mtb_tc_conv2d_wgrad_supported(int, int, int, int, int, int, int, int, int, int, int, const float*, const float*, const float*) { return false; }
-int mtb_tc_conv2d_wgrad_f32(int, int, int, int, int, int, int, int, int, int, int, const float*, const float*, float*, void*, long long, void*) {
-  return mtb_fail(MTB_ERR_UNSUPPORTED, "tensor-core conv wgrad not built");
+// ------------------------------------------------------------------------------ weight gradient
+//
+// dW^T[(tap, ci), co] = sum over output pixels m of patch(X)[m, (tap, ci)] * dY[m, co].
+// Both operands are "MN-major" in memory (for a fixed pixel, channels are contiguous), so they
+// are staged exactly as they lie: the A tile is 4 im2col-mode loads of 32 pixels x 32 channels
+// (one per (tap, channel-block)), the B tile BN/32 boxes of 32 pixels x 32 output channels.
+// The reduction runs over pixels, which is long (up to N*OH*OW) while the output is small, so
+// the pixel range is split across CTAs; each writes an fp32 partial to scratch and a second
+// kernel adds the partials in a fixed order and transposes into dW[co][tap][ci].
+namespace {
+
+struct WgradParams {
+  int Kw;            // KH*KW*Cin: rows of the transposed gradient
+  int Cout;
+  int chunks;        // Kw / 32
+  int cchunks;       // Cin / 32
+  int m_tiles, n_tiles, splits;
+  int kb_total;      // ceil(pixels / 32)
+  int kb_per_split;
+  int OW, OH, SW, SH, PW, PH, KW;
+  float* partial;    // [splits][Kw][Cout]
+};
+
+template <int BN>
+__global__ void __launch_bounds__(192, 1)
+tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapDY, const WgradParams p) {
+  using C = Cfg<BN>;
+  constexpr int STAGES = C::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[8], bar_empty[8], bar_tfull[2], bar_tempty[2];
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tfull[b]), 1);
+      mbar_init(smem_u32(&bar_tempty[b]), 128);
+    }
+    abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int units = p.m_tiles * p.n_tiles * p.splits;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      prefetch_tensormap(&mapX);
+      prefetch_tensormap(&mapDY);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x) {
+        const int split = unit % p.splits, tile = unit / p.splits;
+        const int m_tile = tile / p.n_tiles, n0 = (tile % p.n_tiles) * BN;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
+        int valid = p.chunks - m_tile * 4;
+        if (valid > 4) valid = 4;
+        const uint32_t bytes = (uint32_t)valid * 4096u + C::kBBytes;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 11)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          mbar_expect_tx(full, bytes);
+          const uint32_t a_dst = smem_base + stage * C::kStageBytes, b_dst = a_dst + C::kABytes;
+          const int m = kb * 32;
+          const int ow = m % p.OW, t = m / p.OW;
+          const int pw_ = ow * p.SW - p.PW, ph_ = (t % p.OH) * p.SH - p.PH, pn_ = t / p.OH;
+          for (int q = 0; q < valid; ++q) {
+            const int chunk = m_tile * 4 + q;
+            const int tap = chunk / p.cchunks, cc = chunk - tap * p.cchunks;
+            const int kh = tap / p.KW, kw = tap - kh * p.KW;
+            tma_load_im2col_4d(a_dst + q * 4096, &mapX, full, cc * 32, pw_, ph_, pn_, (uint16_t)kw, (uint16_t)kh);
+          }
+#pragma unroll
+          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapDY, full, n0 + 32 * j, m);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_tf32(128, BN, 1, 1);
+      int stage = 0;
+      uint32_t phase = 0;
+      int t = 0;
+      bool ok = true;
+      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++t) {
+        const int split = unit % p.splits;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
+        const int buf = t & 1;
+        const uint32_t use = (uint32_t)(t >> 1);
+        if (!mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 12)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + buf * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 13)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t a_addr = smem_base + stage * C::kStageBytes, b_addr = a_addr + C::kABytes;
+#pragma unroll
+          for (int kk = 0; kk < 4; ++kk) {
+            mma_tf32(d_tmem, smem_desc_mnmajor(a_addr + kk * 1024, 4096, 512), smem_desc_mnmajor(b_addr + kk * 1024, 4096, 512), idesc,
+                     (kb > kb0 || kk > 0) ? 1u : 0u);
+          }
+          mma_commit(smem_u32(&bar_empty[stage]));
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) mma_commit(smem_u32(&bar_tfull[buf]));
+      }
+    }
+  } else {
+    const int quarter = warp & 3;
+    int t = 0;
+    for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++t) {
+      const int split = unit % p.splits, tile = unit / p.splits;
+      const int m_tile = tile / p.n_tiles, n0 = (tile % p.n_tiles) * BN;
+      const int kb0 = split * p.kb_per_split;
+      const bool empty_unit = kb0 >= p.kb_total;  // cannot happen with the host's split choice; kept for safety
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      bool ok = mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 14);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      const int row = m_tile * 128 + quarter * 32 + lane;
+      float* orow = p.partial + ((long long)split * p.Kw + row) * p.Cout;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (row < p.Kw && col0 < p.Cout) {
+          if (col0 + 32 <= p.Cout) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (empty_unit) v = make_float4(0.f, 0.f, 0.f, 0.f);
+              *reinterpret_cast<float4*>(orow + col0 + j) = v;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.Cout) orow[col0 + j] = empty_unit ? 0.f : __uint_as_float(r[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(smem_u32(&bar_tempty[buf]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// dw[co][r] = sum_s partial[s][r][co]: 32x32 tiles, coalesced reads along co, smem transpose,
+// coalesced writes along r; splits added in index order.
+__global__ void __launch_bounds__(256) wgrad_reduce_transpose_kernel(const float* __restrict__ partial, float* __restrict__ dw, int Kw, int Cout,
+                                                                      int splits) {
+  __shared__ float tile[32][33];
+  const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  const long long plane = (long long)Kw * Cout;
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int r = r0 + j, c = c0 + threadIdx.x;
+    float s = 0.f;
+    if (r < Kw && c < Cout) {
+      const float* q = partial + (long long)r * Cout + c;
+      for (int z = 0; z < splits; ++z) s += q[z * plane];
+    }
+    tile[j][threadIdx.x] = s;
+  }
+  __syncthreads();
+  for (int j = threadIdx.y; j < 32; j += 8) {
+    const int c = c0 + j, r = r0 + threadIdx.x;
+    if (r < Kw && c < Cout) dw[(long long)c * Kw + r] = tile[threadIdx.x][j];
+  }
+}
+
+struct WgradPlan {
+  int bn, m_tiles, n_tiles, splits, kb_total, kb_per_split;
+  long long Kw, pixels;
+};
+
+WgradPlan wgrad_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
+  WgradPlan q;
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  q.pixels = (long long)n * oh * ow;
+  q.Kw = (long long)kh * kw * cin;
+  q.bn = pick_bn(cout);
+  q.m_tiles = (int)((q.Kw + 127) / 128);
+  q.n_tiles = (cout + q.bn - 1) / q.bn;
+  q.kb_total = (int)((q.pixels + 31) / 32);
+  const int tiles = q.m_tiles * q.n_tiles;
+  int splits = (mtb_sm_count() + tiles - 1) / tiles;
+  const int max_splits = (q.kb_total + 7) / 8;  // at least 8 reduction blocks per CTA
+  if (splits > max_splits) splits = max_splits;
+  if (splits < 1) splits = 1;
+  q.kb_per_split = (q.kb_total + splits - 1) / splits;
+  q.splits = (q.kb_total + q.kb_per_split - 1) / q.kb_per_split;  // no empty split
+  return q;
+}
+
+}  // namespace
+
+long long mtb_tc_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
+  if (cin % 32) return 0;
+  WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  return (long long)q.splits * q.Kw * cout * 4 + 256;
+}
+
+bool mtb_tc_conv2d_wgrad_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                   const float* dy, const float* dw) {
+  if (getenv("MTB_DISABLE_TC")) return false;
+  if (!al16(x) || !al16(dy) || !al16(dw)) return false;
+  if (cin % 32 || cout % 4) return false;
+  if (sh > 8 || sw > 8 || ph > 100 || pw > 100 || kh > 32 || kw > 32) return false;
+  if ((long long)n * h * w * cin * 4 < kMinIm2colBytes) return false;
+  return true;
+}
+
+int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                            const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream) {
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  MTB_REQUIRE(workspace && workspace_bytes >= (long long)q.splits * q.Kw * cout * 4, "conv2d_wgrad: workspace too small");
+  CUtensorMap mapX, mapDY;
+  int rc = tc::encode_im2col_4d(&mapX, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 32, true);
+  if (rc) return rc;
+  rc = tc::encode_tiled_2d(&mapDY, dy, q.pixels, cout, cout, 32, 32, true);
+  if (rc) return rc;
+  WgradParams p{};
+  p.Kw = (int)q.Kw; p.Cout = cout; p.chunks = (int)(q.Kw / 32); p.cchunks = cin / 32;
+  p.m_tiles = q.m_tiles; p.n_tiles = q.n_tiles; p.splits = q.splits; p.kb_total = q.kb_total; p.kb_per_split = q.kb_per_split;
+  p.OW = ow; p.OH = oh; p.SW = sw; p.SH = sh; p.PW = pw; p.PH = ph; p.KW = kw;
+  p.partial = (float*)workspace;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int units = q.m_tiles * q.n_tiles * q.splits;
+  const int grid = units < mtb_sm_count() ? units : mtb_sm_count();
+#define MTB_LAUNCH_WGRAD(BN_)                                                                                           \
+  do {                                                                                                                  \
+    static bool configured = false;                                                                                     \
+    if (!configured) {                                                                                                  \
+      MTB_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN_>::kSmemBytes)); \
+      configured = true;                                                                                                \
+    }                                                                                                                   \
+    tc_wgrad_kernel<BN_><<<grid, 192, Cfg<BN_>::kSmemBytes, st>>>(mapX, mapDY, p);                                      \
+  } while (0)
+  if (q.bn == 64) MTB_LAUNCH_WGRAD(64);
+  else if (q.bn == 128) MTB_LAUNCH_WGRAD(128);
+  else MTB_LAUNCH_WGRAD(256);
+#undef MTB_LAUNCH_WGRAD
+  MTB_LAUNCH_CHECK("tc_wgrad_kernel");
+  dim3 rgrid((unsigned)((q.Kw + 31) / 32), (unsigned)((cout + 31) / 32));
+  wgrad_reduce_transpose_kernel<<<rgrid, dim3(32, 8), 0, st>>>((const float*)workspace, dw, (int)q.Kw, cout, q.splits);
+  MTB_LAUNCH_CHECK("wgrad_reduce_transpose_kernel");
+  return MTB_OK;
 }

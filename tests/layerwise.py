@@ -1,0 +1,126 @@
+"""Layer-by-layer ("teacher-forced") parity inside a whole model.
+
+While a model runs forward and backward on the GPU, every operator call is intercepted; its
+inputs are downloaded, the NumPy oracle computes the same operator from those very inputs,
+and outputs / returned gradients are compared.  Because both sides start from identical
+inputs at every layer, the comparison is not amplified by the network depth (nor by ReLU
+masks that flip under rounding), so each operator can be held to its own tolerance: 5e-3 for
+the TF32 tensor-core convolutions and GEMMs, 1e-5 for fp32 operators, bit-exact for pooling.
+"""
+import numpy as np
+
+from conftest import rel_err
+from oracle import ops as O
+
+TF32_TOL = 5e-3
+FP32_TOL = 2e-5
+
+
+def _h(t):
+    return None if t is None else t.to("cpu")._numpy()
+
+
+class LayerwiseChecker:
+    def __init__(self):
+        from mytorch_b200.autograd import DAGTracker
+
+        self.tracker = DAGTracker.instance()
+        self.report = []  # (phase, op, worst relative error)
+
+    def _note(self, phase, op, got, want, tol):
+        err = rel_err(got, want)
+        self.report.append((phase, op, err))
+        assert err <= tol, (phase, op, err, tol)
+
+    # ---- forward: called from the patched add_node
+    def _forward(self, name, inputs, outputs, helpers):
+        y = _h(outputs[0].detach())
+        if name == "conv2d":
+            x, w, b, s, p = inputs
+            self._note("fwd", name, y, O.conv2d_forward(_h(x.detach()), _h(w.detach()), _h(b.detach()) if b is not None else None, s, p), TF32_TOL)
+        elif name == "linear":
+            x, w, b = inputs
+            self._note("fwd", name, y, O.linear_forward(_h(x.detach()), _h(w.detach()), _h(b.detach()) if b is not None else None), TF32_TOL)
+        elif name == "batch_norm2d":
+            x, g, b, eps = inputs
+            ry, mean, var, _, _ = O.batch_norm2d_forward(_h(x.detach()), _h(g.detach()), _h(b.detach()), eps, True, 0.1, None, None)
+            self._note("fwd", name, y, ry, FP32_TOL)
+            self._note("fwd", name + ".mean", _h(helpers[0]), mean.reshape(-1), FP32_TOL)
+            self._note("fwd", name + ".var", _h(helpers[1]), var.reshape(-1), FP32_TOL)
+        elif name == "relu":
+            assert np.array_equal(y, O.relu_forward(_h(inputs[0].detach())))
+        elif name == "max_pool2d":
+            x, k, s, p = inputs
+            assert np.array_equal(y, O.max_pool2d_forward(_h(x.detach()), k, s if s is not None else k, p))
+        elif name == "add":
+            self._note("fwd", name, y, O.add_forward(_h(inputs[0].detach()), _h(inputs[1].detach()), inputs[2]), FP32_TOL)
+        elif name == "sum_scale":
+            x, dim, keep, scale = inputs
+            self._note("fwd", name, y, O.sum_scale_forward(_h(x.detach()), dim, keep, scale), FP32_TOL)
+        elif name == "cross_entropy":
+            self._note("fwd", name, y.reshape(()), O.cross_entropy_forward(_h(inputs[0].detach()), _h(inputs[1])), FP32_TOL)
+
+    # ---- backward: wraps every registered backward function
+    def _backward(self, name, func):
+        def wrapped(*args):
+            grads = func(*args)
+            g = [_h(t) if t is not None and hasattr(t, "shape") else None for t in grads]
+            if name == "conv2d":
+                dy, x, w, b, s, p = args
+                rdx, rdw, rdb = O.conv2d_backward(_h(dy), _h(x.detach()), _h(w.detach()), b is not None, s, p)
+                if g[0] is not None:
+                    self._note("bwd", name + ".dx", g[0], rdx, TF32_TOL)
+                self._note("bwd", name + ".dw", g[1], rdw, TF32_TOL)
+                if b is not None:
+                    self._note("bwd", name + ".db", g[2], rdb, FP32_TOL * 5)
+            elif name == "linear":
+                dy, x, w, b = args
+                rdx, rdw, rdb = O.linear_backward(_h(dy), _h(x.detach()), _h(w.detach()), b is not None)
+                if g[0] is not None:
+                    self._note("bwd", name + ".dx", g[0], rdx, TF32_TOL)
+                self._note("bwd", name + ".dw", g[1], rdw, TF32_TOL)
+                if b is not None:
+                    self._note("bwd", name + ".db", g[2], rdb, FP32_TOL * 5)
+            elif name == "batch_norm2d":
+                dy, mean, var, x, gam, b, eps = args
+                c = x.shape[1]
+                rdx, rdg, rdb = O.batch_norm2d_backward(_h(dy), _h(mean).reshape(1, c, 1, 1), _h(var).reshape(1, c, 1, 1), _h(x.detach()),
+                                                        _h(gam.detach()), eps)
+                self._note("bwd", name + ".dx", g[0], rdx, FP32_TOL * 2)
+                self._note("bwd", name + ".dgamma", g[1], rdg, FP32_TOL * 3)
+                self._note("bwd", name + ".dbeta", g[2], rdb, FP32_TOL * 3)
+            elif name == "relu":
+                assert np.array_equal(g[0], O.relu_backward(_h(args[0]), _h(args[1].detach())))
+            elif name == "max_pool2d":
+                dy, out, x, k, s, p = args
+                self._note("bwd", name, g[0], O.max_pool2d_backward(_h(dy), _h(out.detach()), _h(x.detach()), k, s if s is not None else k, p), 1e-6)
+            elif name == "sum_scale":
+                dy, x, dim, keep, scale = args
+                self._note("bwd", name, g[0], O.sum_scale_backward(_h(dy), x.shape, dim, keep, scale), FP32_TOL)
+            elif name == "cross_entropy":
+                dy, z, t = args
+                self._note("bwd", name, g[0], O.cross_entropy_backward(_h(dy).reshape(()), _h(z.detach()), _h(t)), FP32_TOL)
+            return grads
+
+        return wrapped
+
+    def __enter__(self):
+        self._add_node = self.tracker.add_node
+        self._funcs = dict(self.tracker._backward_funcs)
+
+        def add_node(name, inputs, outputs, helpers=None):
+            self._forward(name, inputs, outputs, helpers or [])
+            return self._add_node(name, inputs, outputs, helpers)
+
+        self.tracker.add_node = add_node
+        for name, f in self._funcs.items():
+            self.tracker._backward_funcs[name] = self._backward(name, f)
+        return self
+
+    def __exit__(self, *exc):
+        self.tracker.add_node = self._add_node
+        self.tracker._backward_funcs.update(self._funcs)
+        return False
+
+    def worst(self, prefix):
+        return max((e for ph, op, e in self.report if op.startswith(prefix)), default=0.0)
