@@ -61,9 +61,11 @@ long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w);
 int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps, int training,
                                  double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var, int relu,
                                  void* workspace, long long workspace_bytes, void* stream);
+/* relu != 0 in forward fuses max(0, .) into the normalise pass; the same flag in backward masks dy where
+ * gamma*xhat + beta < 0 (recomputed, so the ReLU output need not be kept).  beta may be NULL (= 0). */
 int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
-                                  const float* gamma, double eps, float* dx, float* dgamma, float* dbeta, void* workspace,
-                                  long long workspace_bytes, void* stream);
+                                  const float* gamma, const float* beta, double eps, int relu, float* dx, float* dgamma, float* dbeta,
+                                  void* workspace, long long workspace_bytes, void* stream);
 
 /* ---- MaxPool2d (replaces max_pool2d_reference / max_pool2d_backward_reference,
  *      mytorch/native/cuda/pool_ops.cu/1.template:5-52 and 2.template:5-50) ----
@@ -86,6 +88,10 @@ int mtb_relu_forward_f32(const float* x, float* y, long long n, void* stream);
 int mtb_relu_backward_f32(const float* dy, const float* x, float* dx, long long n, void* stream); /* blocks only x < 0 */
 int mtb_add_f32(const float* x, const float* y, float* z, long long n, float alpha, void* stream); /* z = x + alpha*y */
 int mtb_mul_f32(const float* x, const float* y, float* z, long long n, void* stream);
+/* residual add + ReLU in one pass (the reference runs add_reference then relu_reference), and its gradient
+ * g = (x + y < 0) ? 0 : dy, which is the gradient for both operands */
+int mtb_add_relu_f32(const float* x, const float* y, float* z, long long n, void* stream);
+int mtb_add_relu_backward_f32(const float* dy, const float* x, const float* y, float* g, long long n, void* stream);
 int mtb_add_bias_rows_f32(const float* x, const float* bias, float* y, long long rows, int cols, float alpha, void* stream);
 /* general broadcast op over <= 6 logical dims; shape/strides are HOST arrays (strides in elements, 0 broadcasts);
  * op: 0 add, 1 sub, 2 mul, 3 div, 4 pow, 5 alpha*x (replaces broadcast(), broadcast_utils.cuh:4-37, and

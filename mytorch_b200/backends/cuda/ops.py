@@ -242,19 +242,30 @@ def cuda_mm_backward(output_grad, x, y):
 # ---------------------------------------------------------------------------- batch norm
 
 @_reg("cuda", "batch_norm2d")
-def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, running_var):
+def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, running_var, relu=False):
     _f32(x, weight, bias, running_mean, running_var)
     env = _env(x)
     n, c, h, w = x.shape
     y, mean, var = _new(x.shape, x), _new((c,), x), _new((c,), x)
     ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
     env.lib.batch_norm2d_forward_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), int(bool(training)), float(momentum),
-                                     _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), 0, ws, ws_bytes, env.stream())
+                                     _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), int(bool(relu)), ws, ws_bytes, env.stream())
     return y, mean, var
 
 
+@_reg("cuda", "batch_norm2d_relu")
+def cuda_batch_norm2d_relu(x, weight, bias, eps, training, momentum, running_mean, running_var):
+    """BatchNorm2d followed by ReLU in one normalise pass (the ReLU input is never stored)."""
+    return cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, running_var, relu=True)
+
+
+@_reg("cuda", "batch_norm2d_relu_backward")
+def cuda_batch_norm2d_relu_backward(output_grad, mean, var, x, weight, bias, eps):
+    return cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps, relu=True)
+
+
 @_reg("cuda", "batch_norm2d_backward")
-def cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps):
+def cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps, relu=False):
     env = _env(x)
     n, c, h, w = x.shape
     dx = _new(x.shape, x)
@@ -262,8 +273,8 @@ def cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps):
     dg = _new((c,), x) if affine else None
     db = _new((c,), x) if affine else None
     ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
-    env.lib.batch_norm2d_backward_f32(n, c, h, w, _ptr(output_grad), _ptr(mean), _ptr(var), _ptr(x), _ptr(weight), float(eps),
-                                      _ptr(dx), _ptr(dg), _ptr(db), ws, ws_bytes, env.stream())
+    env.lib.batch_norm2d_backward_f32(n, c, h, w, _ptr(output_grad), _ptr(mean), _ptr(var), _ptr(x), _ptr(weight), _ptr(bias), float(eps),
+                                      int(bool(relu)), _ptr(dx), _ptr(dg), _ptr(db), ws, ws_bytes, env.stream())
     return [dx, dg, db]
 
 
@@ -333,6 +344,28 @@ def cuda_relu_backward(output_grad, x):
     dx = _new(x.shape, x)
     env.lib.relu_backward_f32(_ptr(output_grad), _ptr(x), _ptr(dx), _numel(x.shape), env.stream())
     return [dx]
+
+
+@_reg("cuda", "add_relu")
+def cuda_add_relu(x, y):
+    """max(0, x + y) for same-shape operands (residual connection followed by ReLU)."""
+    _f32(x, y)
+    if x.shape != y.shape:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([x.shape, y.shape])
+    env = _env(x)
+    z = _new(x.shape, x)
+    env.lib.add_relu_f32(_ptr(x), _ptr(y), _ptr(z), _numel(x.shape), env.stream())
+    return z
+
+
+@_reg("cuda", "add_relu_backward")
+def cuda_add_relu_backward(output_grad, x, y):
+    env = _env(x)
+    g = _new(x.shape, x)
+    env.lib.add_relu_backward_f32(_ptr(output_grad), _ptr(x), _ptr(y), _ptr(g), _numel(x.shape), env.stream())
+    return g, g  # one tensor serves both operands: gradients are never modified in place
 
 
 @_reg("cuda", "fill")

@@ -84,9 +84,9 @@ __global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __re
   }
 }
 
-// One warp per channel: lane l merges partials l, l+32, ... in order, then the 32 lane results
-// are merged by a fixed shuffle tree (Chan's parallel update), so the result does not depend
-// on scheduling.  Writes the batch mean / biased variance, the per-channel scale
+// Eight threads per channel: thread g merges partials g, g+8, ... in order (Chan's parallel
+// update), then the eight results are merged in index order, so the result does not depend on
+// scheduling.  Writes the batch mean / biased variance, the per-channel scale
 // gamma/sqrt(var+eps) used by the normalise pass, and blends the running statistics.
 __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, float nb, float mb, float qb) {
   if (nb == 0.f) return;
@@ -101,22 +101,21 @@ __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, flo
 __global__ void __launch_bounds__(256) bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
                                                               float one_minus_m, float m, float* running_mean, float* running_var,
                                                               float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
-  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
-  int lane = threadIdx.x & 31;
-  if (c >= C) return;
+  // 32 channels x 8 partial-groups per CTA: consecutive threads read consecutive channels.
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float n = 0.f, mean = 0.f, m2 = 0.f;
-  for (int p = lane; p < P; p += 32) {
-    const float* q = partial + (long long)p * 3 * C + c;
-    chan_merge(n, mean, m2, q[0], q[C], q[2 * C]);
+  if (c < C) {
+    for (int p = py; p < P; p += 8) {
+      const float* q = partial + (long long)p * 3 * C + c;
+      chan_merge(n, mean, m2, q[0], q[C], q[2 * C]);
+    }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    float nb = __shfl_down_sync(0xffffffffu, n, o);
-    float mb = __shfl_down_sync(0xffffffffu, mean, o);
-    float qb = __shfl_down_sync(0xffffffffu, m2, o);
-    chan_merge(n, mean, m2, nb, mb, qb);
-  }
-  if (lane != 0) return;
+  __shared__ float sn[8][32], smean[8][32], sm2[8][32];
+  sn[py][cx] = n; smean[py][cx] = mean; sm2[py][cx] = m2;
+  __syncthreads();
+  if (py != 0 || c >= C) return;
+  for (int k = 1; k < 8; ++k) chan_merge(n, mean, m2, sn[k][cx], smean[k][cx], sm2[k][cx]);
   float mu = mean;
   float var = n > 0.f ? m2 / n : 0.f;
   mean_out[c] = mu;
@@ -174,21 +173,26 @@ __global__ void __launch_bounds__(256) bn_normalize_kernel(const float* __restri
 // ---------------------------------------------------------------- backward
 
 // partial[p][0][c] = sum dy, partial[p][1][c] = sum dy * xhat over the CTA's rows.
-template <int V>
+// RELU: the forward output went through max(0, .) in the same pass; the upstream gradient is
+// first masked where the (recomputed, bit-identical) normalised value is negative.
+template <int V, bool RELU>
 __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __restrict__ dy, const float* __restrict__ x, long long rows, int C, int L,
                                                               long long rows_per_block, const float* __restrict__ mean,
-                                                              const float* __restrict__ var, float eps, float* __restrict__ partial) {
+                                                              const float* __restrict__ var, float eps, const float* __restrict__ gamma,
+                                                              const float* __restrict__ beta, float* __restrict__ partial) {
   const int lane = threadIdx.x & (L - 1);
   const int rsub = threadIdx.x / L;
   const int R = 256 / L;
   const int cg = blockIdx.x * L + lane;
   const bool active = cg * V < C;
-  float mu[V], rstd[V], a0[V], a1[V];
+  float mu[V], rstd[V], a0[V], a1[V], gs[V], bt[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     a0[i] = 0.f; a1[i] = 0.f;
     mu[i] = active ? mean[cg * V + i] : 0.f;
     rstd[i] = active ? 1.0f / sqrtf(var[cg * V + i] + eps) : 0.f;
+    gs[i] = (active && gamma) ? gamma[cg * V + i] * rstd[i] : rstd[i];
+    bt[i] = (active && beta) ? beta[cg * V + i] : 0.f;
   }
   long long r0 = blockIdx.y * rows_per_block;
   long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
@@ -200,8 +204,10 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
       VecF<V> f = vload<V>(x + off);
 #pragma unroll
       for (int i = 0; i < V; ++i) {
-        a0[i] += g.v[i];
-        a1[i] += g.v[i] * ((f.v[i] - mu[i]) * rstd[i]);
+        float gi = g.v[i];
+        if (RELU && (f.v[i] - mu[i]) * gs[i] + bt[i] < 0.f) gi = 0.f;
+        a0[i] += gi;
+        a1[i] += gi * ((f.v[i] - mu[i]) * rstd[i]);
       }
     }
   }
@@ -222,24 +228,24 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
 }
 
 // dbeta = sum dy, dgamma = sum dy*xhat; coefficients for dx = k1 * (dy - k2 - (x - mean) * k3).
-// One warp per channel, fixed summation order.
+// Eight threads per channel, fixed summation order.
 __global__ void __launch_bounds__(256) bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
                                                             const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
                                                             float* __restrict__ dbeta, float* __restrict__ coef) {
-  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
-  int lane = threadIdx.x & 31;
-  if (c >= C) return;
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s0 = 0.f, s1 = 0.f;
-  for (int p = lane; p < P; p += 32) {
-    s0 += partial[(long long)p * 2 * C + c];
-    s1 += partial[(long long)p * 2 * C + C + c];
+  if (c < C) {
+    for (int p = py; p < P; p += 8) {
+      s0 += partial[(long long)p * 2 * C + c];
+      s1 += partial[(long long)p * 2 * C + C + c];
+    }
   }
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) {
-    s0 += __shfl_down_sync(0xffffffffu, s0, o);
-    s1 += __shfl_down_sync(0xffffffffu, s1, o);
-  }
-  if (lane != 0) return;
+  __shared__ float t0[8][32], t1[8][32];
+  t0[py][cx] = s0; t1[py][cx] = s1;
+  __syncthreads();
+  if (py != 0 || c >= C) return;
+  for (int k = 1; k < 8; ++k) { s0 += t0[k][cx]; s1 += t1[k][cx]; }
   float db = s0, dg = s1;
   if (dbeta) dbeta[c] = db;
   if (dgamma) dgamma[c] = dg;
@@ -250,22 +256,24 @@ __global__ void __launch_bounds__(256) bn_bwd_final_kernel(const float* __restri
   coef[2 * C + c] = rstd * dg * inv_m;  // k3: (x - mean) * k3 = xhat * dgamma / m
 }
 
-template <int V>
+template <int V, bool RELU>
 __global__ void __launch_bounds__(256) bn_bwd_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x, float* __restrict__ dx,
                                                          long long rows, int C, int L, long long rows_per_block,
-                                                         const float* __restrict__ mean, const float* __restrict__ coef) {
+                                                         const float* __restrict__ mean, const float* __restrict__ coef,
+                                                         const float* __restrict__ beta) {
   const int lane = threadIdx.x & (L - 1);
   const int rsub = threadIdx.x / L;
   const int R = 256 / L;
   const int cg = blockIdx.x * L + lane;
   if (cg * V >= C) return;
-  float mu[V], k1[V], k2[V], k3[V];
+  float mu[V], k1[V], k2[V], k3[V], bt[V];
 #pragma unroll
   for (int i = 0; i < V; ++i) {
     mu[i] = mean[cg * V + i];
     k1[i] = coef[cg * V + i];
     k2[i] = coef[C + cg * V + i];
     k3[i] = coef[2 * C + cg * V + i];
+    bt[i] = beta ? beta[cg * V + i] : 0.f;
   }
   long long r0 = blockIdx.y * rows_per_block;
   long long r1 = r0 + rows_per_block < rows ? r0 + rows_per_block : rows;
@@ -275,7 +283,11 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_kernel(const float* __restrict_
     VecF<V> g = vload<V>(dy + off);
     VecF<V> f = vload<V>(x + off);
 #pragma unroll
-    for (int i = 0; i < V; ++i) g.v[i] = k1[i] * (g.v[i] - k2[i] - (f.v[i] - mu[i]) * k3[i]);
+    for (int i = 0; i < V; ++i) {
+      float gi = g.v[i];
+      if (RELU && (f.v[i] - mu[i]) * k1[i] + bt[i] < 0.f) gi = 0.f;  // k1 = gamma / sigma, the forward's scale
+      g.v[i] = k1[i] * (gi - k2[i] - (f.v[i] - mu[i]) * k3[i]);
+    }
     vstore<V>(dx + off, g);
   }
 }
@@ -326,7 +338,7 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
     if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
-    bn_stats_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+    bn_stats_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
                                                       running_mean, running_var, mean, var, scale);
     MTB_LAUNCH_CHECK("bn_stats_final_kernel");
   } else {
@@ -347,9 +359,11 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
 }
 
 // dx = gamma/sigma * (dy - dbeta/m - xhat * dgamma/m); dgamma, dbeta may be NULL (not affine).
+// relu != 0: backward of the fused forward (relu flag set there); dy is masked where the
+// normalised value gamma*xhat+beta is negative, which needs beta (NULL = 0).
 MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
-                                          const float* gamma, double eps, float* dx, float* dgamma, float* dbeta, void* workspace,
-                                          long long workspace_bytes, void* stream) {
+                                          const float* gamma, const float* beta, double eps, int relu, float* dx, float* dgamma,
+                                          float* dbeta, void* workspace, long long workspace_bytes, void* stream) {
   MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && dy && mean && var && x && dx && workspace, "batch_norm2d_backward: bad arguments");
   MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_backward: workspace too small");
   cudaStream_t st = (cudaStream_t)stream;
@@ -359,16 +373,21 @@ MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const floa
   float* coef = partial + (long long)mtb_col_max_partials() * 3 * c;  // 3*C floats fit in the 4*C tail
   ColCfg cfg = mtb_col_cfg(rows, c, aligned);
   dim3 grid(cfg.col_blocks, cfg.row_blocks);
-  if (cfg.vec == 4) bn_bwd_partial_kernel<4><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
-  else bn_bwd_partial_kernel<1><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, partial);
+#define MTB_BN_PARTIAL(V_, R_) \
+  bn_bwd_partial_kernel<V_, R_><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, gamma, beta, partial)
+  if (cfg.vec == 4) { if (relu) MTB_BN_PARTIAL(4, true); else MTB_BN_PARTIAL(4, false); }
+  else { if (relu) MTB_BN_PARTIAL(1, true); else MTB_BN_PARTIAL(1, false); }
+#undef MTB_BN_PARTIAL
   MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
-  bn_bwd_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+  bn_bwd_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
                                                           dgamma, dbeta, coef);
   MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
   ColCfg s = stream_cfg(rows, c, aligned);
   dim3 g2(s.col_blocks, s.row_blocks);
-  if (s.vec == 4) bn_bwd_dx_kernel<4><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef);
-  else bn_bwd_dx_kernel<1><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef);
+#define MTB_BN_DX(V_, R_) bn_bwd_dx_kernel<V_, R_><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef, beta)
+  if (s.vec == 4) { if (relu) MTB_BN_DX(4, true); else MTB_BN_DX(4, false); }
+  else { if (relu) MTB_BN_DX(1, true); else MTB_BN_DX(1, false); }
+#undef MTB_BN_DX
   MTB_LAUNCH_CHECK("bn_bwd_dx_kernel");
   return MTB_OK;
 }

@@ -36,9 +36,26 @@ struct ReluF { __device__ float operator()(float x) const { return fmaxf(x, 0.f)
 // Gradient is blocked only for x < 0 (the CPU reference passes it at x == 0).
 struct ReluBwdF { __device__ float operator()(float dy, float x) const { return x < 0.f ? 0.f : dy; } };
 struct AxpyF { float alpha; __device__ float operator()(float x, float y) const { return x + y * alpha; } };
+struct AddReluF { __device__ float operator()(float x, float y) const { return fmaxf(x + y, 0.f); } };
 struct MulF { __device__ float operator()(float x, float y) const { return x * y; } };
 struct ScaleF { float s; __device__ float operator()(float x) const { return x * s; } };
 struct CopyF { __device__ float operator()(float x) const { return x; } };
+
+// g = (x + y < 0) ? 0 : dy — backward of max(0, x + y); the sum is recomputed from the two
+// forward inputs (bit-identical to the forward's), and a sum of exactly 0 passes the gradient.
+__global__ void __launch_bounds__(kThreads) add_relu_bwd_kernel(float* g, const float* dy, const float* x, const float* y, long long n4, long long n) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long v = i; v < n4; v += stride) {
+    float4 d = ld4(dy + 4 * v), a = ld4(x + 4 * v), b = ld4(y + 4 * v);
+    d.x = (a.x + b.x < 0.f) ? 0.f : d.x;
+    d.y = (a.y + b.y < 0.f) ? 0.f : d.y;
+    d.z = (a.z + b.z < 0.f) ? 0.f : d.z;
+    d.w = (a.w + b.w < 0.f) ? 0.f : d.w;
+    st4(g + 4 * v, d);
+  }
+  for (long long t = 4 * n4 + i; t < n; t += stride) g[t] = (x[t] + y[t] < 0.f) ? 0.f : dy[t];
+}
 
 template <class F>
 int launch_map1(float* out, const float* a, long long n, F f, cudaStream_t s, const char* name) {
@@ -192,6 +209,23 @@ MTB_API int mtb_relu_backward_f32(const float* dy, const float* x, float* dx, lo
 MTB_API int mtb_add_f32(const float* x, const float* y, float* z, long long n, float alpha, void* stream) {
   MTB_REQUIRE(n >= 0 && ((x && y && z) || n == 0), "add: bad arguments");
   return launch_map2(z, x, y, n, AxpyF{alpha}, (cudaStream_t)stream, "add");
+}
+
+// z = max(0, x + y): residual add and ReLU in one pass.
+MTB_API int mtb_add_relu_f32(const float* x, const float* y, float* z, long long n, void* stream) {
+  MTB_REQUIRE(n >= 0 && ((x && y && z) || n == 0), "add_relu: bad arguments");
+  return launch_map2(z, x, y, n, AddReluF{}, (cudaStream_t)stream, "add_relu");
+}
+
+// g = (x + y < 0) ? 0 : dy: the gradient of max(0, x + y) with respect to x and to y.
+MTB_API int mtb_add_relu_backward_f32(const float* dy, const float* x, const float* y, float* g, long long n, void* stream) {
+  MTB_REQUIRE(n >= 0 && ((dy && x && y && g) || n == 0), "add_relu_backward: bad arguments");
+  if (n == 0) return MTB_OK;
+  bool vec = mtb_aligned16(dy) && mtb_aligned16(x) && mtb_aligned16(y) && mtb_aligned16(g);
+  long long n4 = vec ? n / 4 : 0;
+  add_relu_bwd_kernel<<<mtb_stream_grid(vec ? (n4 > 0 ? n4 : 1) : n, kThreads), kThreads, 0, (cudaStream_t)stream>>>(g, dy, x, y, n4, n);
+  MTB_LAUNCH_CHECK("add_relu_bwd_kernel");
+  return MTB_OK;
 }
 
 MTB_API int mtb_mul_f32(const float* x, const float* y, float* z, long long n, void* stream) {

@@ -41,16 +41,19 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const float* __rest
   }
 }
 
-// One warp per channel, fixed summation order.
+// Eight threads per channel (consecutive threads read consecutive channels), fixed order.
 __global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int P, int C, float scale, float* __restrict__ out) {
-  int c = blockIdx.x * 8 + (threadIdx.x >> 5);
-  int lane = threadIdx.x & 31;
-  if (c >= C) return;
+  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
+  const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  for (int p = lane; p < P; p += 32) s += partial[(long long)p * C + c];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) s += __shfl_down_sync(0xffffffffu, s, o);
-  if (lane == 0) out[c] = s * scale;
+  if (c < C)
+    for (int p = py; p < P; p += 8) s += partial[(long long)p * C + c];
+  __shared__ float t[8][32];
+  t[py][cx] = s;
+  __syncthreads();
+  if (py != 0 || c >= C) return;
+  for (int k = 1; k < 8; ++k) s += t[k][cx];
+  out[c] = s * scale;
 }
 
 // y[n, c] = scale * sum_{hw} x[n, hw, c]; one thread per (n, c) with c fastest (coalesced).
@@ -125,7 +128,7 @@ MTB_API int mtb_colsum_f32(const float* a, long long rows, int c, float scale, f
   if (cfg.vec == 4) colsum_partial_kernel<4><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   else colsum_partial_kernel<1><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   MTB_LAUNCH_CHECK("colsum_partial_kernel");
-  colsum_final_kernel<<<mtb_div_up(c, 8), 256, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
+  colsum_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
   MTB_LAUNCH_CHECK("colsum_final_kernel");
   return MTB_OK;
 }

@@ -157,6 +157,27 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t saddr, uint32_t l
   return d;
 }
 
+// The same descriptors as two 32-bit words, so that the issuing thread only has to add a small
+// constant to the low word per MMA (start address lives in bits 0-13 of the low word).
+__host__ __device__ constexpr uint32_t desc_hi_kmajor() { return (1024u >> 4) | (1u << 14) | (2u << 29); }
+__host__ __device__ constexpr uint32_t desc_hi_mnmajor() { return (512u >> 4) | (1u << 14) | (1u << 29); }
+__device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | ((4096u >> 4) << 16); }
+
+__device__ __forceinline__ void mma_tf32_words(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                               uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], da, db, %5, p;\n"
+      "}\n"
+      ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
+}
+
 // Instruction descriptor for kind::tf32, FP32 accumulate, dense, M x N tile.
 __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, int a_mn_major, int b_mn_major) {
   return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)a_mn_major << 15) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |

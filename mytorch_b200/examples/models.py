@@ -6,6 +6,7 @@ then per block conv1, bn1, conv2, bn2, [downsample conv, bn], finally fc) becaus
 initialisation consumes one random draw per weight / bias tensor in creation order.
 """
 import mytorch_b200.nn as nn
+import mytorch_b200.nn.functional as F
 
 
 class Flatten(nn.Module):
@@ -20,11 +21,20 @@ def small_cnn(device="cpu"):
         Flatten(), nn.Linear(9216, 128, device=device), nn.ReLU(), nn.Linear(128, 10, device=device))
 
 
+def _bn_relu(channels, fused, device):
+    """(norm layer, relu-or-None): fused=True folds the ReLU into the BatchNorm kernel."""
+    return (nn.BatchNormReLU2d(channels, device=device), None) if fused else (nn.BatchNorm2d(channels, device=device), nn.ReLU())
+
+
 class BasicBlock(nn.Module):
-    def __init__(self, cin, cout, stride, device="cpu"):
+    """fused=True uses the fused BatchNorm+ReLU and add+ReLU operators (same arithmetic, fewer
+    passes over memory); fused=False composes the six reference layer types one by one."""
+
+    def __init__(self, cin, cout, stride, device="cpu", fused=True):
         super().__init__()
+        self.fused = fused
         self.conv1 = nn.Conv2d(cin, cout, 3, stride, 1, bias=False, device=device)
-        self.bn1 = nn.BatchNorm2d(cout, device=device)
+        self.bn1 = nn.BatchNormReLU2d(cout, device=device) if fused else nn.BatchNorm2d(cout, device=device)
         self.conv2 = nn.Conv2d(cout, cout, 3, 1, 1, bias=False, device=device)
         self.bn2 = nn.BatchNorm2d(cout, device=device)
         self.downsample = None
@@ -34,31 +44,37 @@ class BasicBlock(nn.Module):
         self.relu = nn.ReLU()
 
     def forward(self, x):
-        y = self.bn2(self.conv2(self.relu(self.bn1(self.conv1(x)))))
+        y = self.bn1(self.conv1(x))
+        if not self.fused:
+            y = self.relu(y)
+        y = self.bn2(self.conv2(y))
         shortcut = x if self.downsample is None else self.downsample(x)
-        return self.relu(y + shortcut)
+        return F.add_relu(y, shortcut) if self.fused else self.relu(y + shortcut)
 
 
 class ResNet18Cifar(nn.Module):
     """3x3 stride-1 stem without max-pool, stages of 2 BasicBlocks (strides 1/2/2/2), global
     average pool, Linear."""
 
-    def __init__(self, widths=(64, 128, 256, 512), num_classes=10, device="cpu"):
+    def __init__(self, widths=(64, 128, 256, 512), num_classes=10, device="cpu", fused=True):
         super().__init__()
+        self.fused = fused
         self.conv1 = nn.Conv2d(3, widths[0], 3, 1, 1, bias=False, device=device)
-        self.bn1 = nn.BatchNorm2d(widths[0], device=device)
+        self.bn1 = nn.BatchNormReLU2d(widths[0], device=device) if fused else nn.BatchNorm2d(widths[0], device=device)
         self.relu = nn.ReLU()
         cin = widths[0]
         for si, wd in enumerate(widths):
             blocks = []
             for bi in range(2):
-                blocks.append(BasicBlock(cin, wd, 2 if (si > 0 and bi == 0) else 1, device=device))
+                blocks.append(BasicBlock(cin, wd, 2 if (si > 0 and bi == 0) else 1, device=device, fused=fused))
                 cin = wd
             setattr(self, f"layer{si + 1}", nn.Sequential(*blocks))
         self.fc = nn.Linear(cin, num_classes, device=device)
 
     def forward(self, x):
-        x = self.relu(self.bn1(self.conv1(x)))
+        x = self.bn1(self.conv1(x))
+        if not self.fused:
+            x = self.relu(x)
         x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
         return self.fc(x.mean(dim=(2, 3)))
 

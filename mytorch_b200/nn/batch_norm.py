@@ -2,7 +2,7 @@
 running var 1; training mode normalises with batch statistics and blends the *biased* batch
 variance into ``running_var``."""
 from mytorch_b200.dtype import float32
-from mytorch_b200.nn.functional.batch_norm import _batch_norm2d
+from mytorch_b200.nn.functional.batch_norm import _batch_norm2d, _batch_norm2d_relu
 from mytorch_b200.nn.module import Module
 from mytorch_b200.nn.parameter import Parameter
 from mytorch_b200.tensor import Tensor
@@ -37,3 +37,11 @@ class BatchNorm2d(Module):
 
     def forward(self, x):
         return _batch_norm2d(x, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean, self.running_var)
+
+
+class BatchNormReLU2d(BatchNorm2d):
+    """``BatchNorm2d`` immediately followed by ``ReLU`` as one fused operator.  Same parameters,
+    buffers and state-dict keys as ``BatchNorm2d``; results equal ``ReLU()(BatchNorm2d(...)(x))``."""
+
+    def forward(self, x):
+        return _batch_norm2d_relu(x, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean, self.running_var)

@@ -26,6 +26,7 @@ class LayerwiseChecker:
 
         self.tracker = DAGTracker.instance()
         self.report = []  # (phase, op, worst relative error)
+        self._fused_out = {}
 
     def _note(self, phase, op, got, want, tol):
         err = rel_err(got, want)
@@ -41,9 +42,12 @@ class LayerwiseChecker:
         elif name == "linear":
             x, w, b = inputs
             self._note("fwd", name, y, O.linear_forward(_h(x.detach()), _h(w.detach()), _h(b.detach()) if b is not None else None), TF32_TOL)
-        elif name == "batch_norm2d":
+        elif name in ("batch_norm2d", "batch_norm2d_relu"):
             x, g, b, eps = inputs
             ry, mean, var, _, _ = O.batch_norm2d_forward(_h(x.detach()), _h(g.detach()), _h(b.detach()), eps, True, 0.1, None, None)
+            if name.endswith("relu"):
+                ry = O.relu_forward(ry)
+                self._fused_out[id(x)] = y
             self._note("fwd", name, y, ry, FP32_TOL)
             self._note("fwd", name + ".mean", _h(helpers[0]), mean.reshape(-1), FP32_TOL)
             self._note("fwd", name + ".var", _h(helpers[1]), var.reshape(-1), FP32_TOL)
@@ -54,6 +58,8 @@ class LayerwiseChecker:
             assert np.array_equal(y, O.max_pool2d_forward(_h(x.detach()), k, s if s is not None else k, p))
         elif name == "add":
             self._note("fwd", name, y, O.add_forward(_h(inputs[0].detach()), _h(inputs[1].detach()), inputs[2]), FP32_TOL)
+        elif name == "add_relu":
+            assert np.array_equal(y, O.relu_forward(O.add_forward(_h(inputs[0].detach()), _h(inputs[1].detach()), 1)))
         elif name == "sum_scale":
             x, dim, keep, scale = inputs
             self._note("fwd", name, y, O.sum_scale_forward(_h(x.detach()), dim, keep, scale), FP32_TOL)
@@ -81,16 +87,24 @@ class LayerwiseChecker:
                 self._note("bwd", name + ".dw", g[1], rdw, TF32_TOL)
                 if b is not None:
                     self._note("bwd", name + ".db", g[2], rdb, FP32_TOL * 5)
-            elif name == "batch_norm2d":
+            elif name in ("batch_norm2d", "batch_norm2d_relu"):
                 dy, mean, var, x, gam, b, eps = args
                 c = x.shape[1]
-                rdx, rdg, rdb = O.batch_norm2d_backward(_h(dy), _h(mean).reshape(1, c, 1, 1), _h(var).reshape(1, c, 1, 1), _h(x.detach()),
-                                                        _h(gam.detach()), eps)
+                hm, hv, hx, hdy = _h(mean).reshape(1, c, 1, 1), _h(var).reshape(1, c, 1, 1), _h(x.detach()), _h(dy)
+                if name.endswith("relu"):
+                    # the reference would run relu_backward on the BatchNorm output first; the mask is
+                    # taken from the forward output recorded for this node (y > 0)
+                    hdy = np.where(self._fused_out[id(x)] > 0, hdy, 0).astype(hdy.dtype)
+                rdx, rdg, rdb = O.batch_norm2d_backward(hdy, hm, hv, hx, _h(gam.detach()), eps)
                 self._note("bwd", name + ".dx", g[0], rdx, FP32_TOL * 2)
                 self._note("bwd", name + ".dgamma", g[1], rdg, FP32_TOL * 3)
                 self._note("bwd", name + ".dbeta", g[2], rdb, FP32_TOL * 3)
             elif name == "relu":
                 assert np.array_equal(g[0], O.relu_backward(_h(args[0]), _h(args[1].detach())))
+            elif name == "add_relu":
+                dy, x, y = args
+                want = O.relu_backward(_h(dy), O.add_forward(_h(x.detach()), _h(y.detach()), 1))
+                assert np.array_equal(g[0], want) and np.array_equal(g[1], want)
             elif name == "max_pool2d":
                 dy, out, x, k, s, p = args
                 self._note("bwd", name, g[0], O.max_pool2d_backward(_h(dy), _h(out.detach()), _h(x.detach()), k, s if s is not None else k, p), 1e-6)

@@ -218,3 +218,36 @@ def test_step_is_bitwise_reproducible_and_graph_replay_matches_eager():
     l3, p3 = run(True)
     assert l1 == l2 and all(np.array_equal(a, b) for a, b in zip(p1, p2))
     assert l1 == l3 and all(np.array_equal(a, b) for a, b in zip(p1, p3))
+
+
+def test_fused_and_unfused_models_agree_bitwise():
+    """BatchNorm+ReLU and add+ReLU fused operators compute exactly what the separate operators do."""
+    import gpu_util as g
+    import mytorch_b200 as mt
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.examples.models import ResNet18Cifar
+    from mytorch_b200.optim import SGD
+
+    rng = np.random.default_rng(12)
+    x = rng.standard_normal((16, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, 16).astype(np.int64)
+
+    def run(fused):
+        mt.manual_seed(33)
+        net = ResNet18Cifar((16, 32, 32, 64), fused=fused)
+        net.to(g.DEV)
+        opt = SGD(net.parameters(), lr=0.05, momentum=0.9)
+        losses = []
+        for _ in range(2):
+            loss = F.cross_entropy(net(g.dev(x)), g.dev(t))
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        return losses, [g.host(p.detach()) for p in net.parameters()]
+
+    la, pa = run(True)
+    lb, pb = run(False)
+    assert la == lb
+    for a, b in zip(pa, pb):
+        assert np.array_equal(a, b)
