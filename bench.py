@@ -390,8 +390,18 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
+    ap.add_argument("--only-legs", action="store_true",
+                    help="run only the single-kernel legs (conv fwd/dgrad/wgrad, BatchNorm, ReLU) and print their JSON; "
+                         "this is the command profiled with ncu for the summaries under profiles/")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.only_legs:
+        import torch
+
+        from mytorch_b200.backends.cuda.env import CudaEnv
+
+        roof, kernels = kernel_legs(torch, CudaEnv.instance(), measured_peaks())
+        print(json.dumps({"roofline": roof, "kernels": kernels}))
+    elif args.impl == "reference":
         run_reference_arm(args)
     else:
         run_gpu_arm(args)

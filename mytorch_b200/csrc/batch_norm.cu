@@ -84,8 +84,8 @@ __global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __re
   }
 }
 
-// Eight threads per channel: thread g merges partials g, g+8, ... in order (Chan's parallel
-// update), then the eight results are merged in index order, so the result does not depend on
+// Thirty-two threads per channel: thread g merges partials g, g+32, ... in order (Chan's parallel
+// update), then the 32 results are merged in index order, so the result does not depend on
 // scheduling.  Writes the batch mean / biased variance, the per-channel scale
 // gamma/sqrt(var+eps) used by the normalise pass, and blends the running statistics.
 __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, float nb, float mb, float qb) {
@@ -98,24 +98,35 @@ __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, flo
   n = nt;
 }
 
-__global__ void __launch_bounds__(256) bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
-                                                              float one_minus_m, float m, float* running_mean, float* running_var,
-                                                              float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
-  // 32 channels x 8 partial-groups per CTA: consecutive threads read consecutive channels.
+__global__ void __launch_bounds__(1024) bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
+                                                               float one_minus_m, float m, float* running_mean, float* running_var,
+                                                               float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
+  // 32 channels x 32 partial-groups per CTA: consecutive threads read consecutive channels.
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
   float n = 0.f, mean = 0.f, m2 = 0.f;
   if (c < C) {
-    for (int p = py; p < P; p += 8) {
+    int p = py;
+    for (; p + 96 < P; p += 128) {  // four independent loads in flight before the dependent merges
+      float v[4][3];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float* q = partial + (long long)(p + 32 * u) * 3 * C + c;
+        v[u][0] = q[0]; v[u][1] = q[C]; v[u][2] = q[2 * C];
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) chan_merge(n, mean, m2, v[u][0], v[u][1], v[u][2]);
+    }
+    for (; p < P; p += 32) {
       const float* q = partial + (long long)p * 3 * C + c;
       chan_merge(n, mean, m2, q[0], q[C], q[2 * C]);
     }
   }
-  __shared__ float sn[8][32], smean[8][32], sm2[8][32];
+  __shared__ float sn[32][33], smean[32][33], sm2[32][33];
   sn[py][cx] = n; smean[py][cx] = mean; sm2[py][cx] = m2;
   __syncthreads();
   if (py != 0 || c >= C) return;
-  for (int k = 1; k < 8; ++k) chan_merge(n, mean, m2, sn[k][cx], smean[k][cx], sm2[k][cx]);
+  for (int k = 1; k < 32; ++k) chan_merge(n, mean, m2, sn[k][cx], smean[k][cx], sm2[k][cx]);
   float mu = mean;
   float var = n > 0.f ? m2 / n : 0.f;
   mean_out[c] = mu;
@@ -228,24 +239,25 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
 }
 
 // dbeta = sum dy, dgamma = sum dy*xhat; coefficients for dx = k1 * (dy - k2 - (x - mean) * k3).
-// Eight threads per channel, fixed summation order.
-__global__ void __launch_bounds__(256) bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
-                                                            const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
-                                                            float* __restrict__ dbeta, float* __restrict__ coef) {
+// Thirty-two threads per channel, fixed summation order.
+__global__ void __launch_bounds__(1024) bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
+                                                             const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
+                                                             float* __restrict__ dbeta, float* __restrict__ coef) {
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
   float s0 = 0.f, s1 = 0.f;
   if (c < C) {
-    for (int p = py; p < P; p += 8) {
+#pragma unroll 4
+    for (int p = py; p < P; p += 32) {
       s0 += partial[(long long)p * 2 * C + c];
       s1 += partial[(long long)p * 2 * C + C + c];
     }
   }
-  __shared__ float t0[8][32], t1[8][32];
+  __shared__ float t0[32][33], t1[32][33];
   t0[py][cx] = s0; t1[py][cx] = s1;
   __syncthreads();
   if (py != 0 || c >= C) return;
-  for (int k = 1; k < 8; ++k) { s0 += t0[k][cx]; s1 += t1[k][cx]; }
+  for (int k = 1; k < 32; ++k) { s0 += t0[k][cx]; s1 += t1[k][cx]; }
   float db = s0, dg = s1;
   if (dbeta) dbeta[c] = db;
   if (dgamma) dgamma[c] = dg;
@@ -338,7 +350,7 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
     if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
-    bn_stats_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+    bn_stats_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
                                                       running_mean, running_var, mean, var, scale);
     MTB_LAUNCH_CHECK("bn_stats_final_kernel");
   } else {
@@ -379,7 +391,7 @@ MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const floa
   else { if (relu) MTB_BN_PARTIAL(1, true); else MTB_BN_PARTIAL(1, false); }
 #undef MTB_BN_PARTIAL
   MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
-  bn_bwd_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+  bn_bwd_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
                                                           dgamma, dbeta, coef);
   MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
   ColCfg s = stream_cfg(rows, c, aligned);

@@ -41,18 +41,20 @@ __global__ void __launch_bounds__(256) colsum_partial_kernel(const float* __rest
   }
 }
 
-// Eight threads per channel (consecutive threads read consecutive channels), fixed order.
-__global__ void __launch_bounds__(256) colsum_final_kernel(const float* __restrict__ partial, int P, int C, float scale, float* __restrict__ out) {
+// Thirty-two threads per channel (consecutive threads read consecutive channels), fixed order.
+__global__ void __launch_bounds__(1024) colsum_final_kernel(const float* __restrict__ partial, int P, int C, float scale, float* __restrict__ out) {
   const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
   const int c = blockIdx.x * 32 + cx;
   float s = 0.f;
-  if (c < C)
-    for (int p = py; p < P; p += 8) s += partial[(long long)p * C + c];
-  __shared__ float t[8][32];
+  if (c < C) {
+#pragma unroll 4
+    for (int p = py; p < P; p += 32) s += partial[(long long)p * C + c];
+  }
+  __shared__ float t[32][33];
   t[py][cx] = s;
   __syncthreads();
   if (py != 0 || c >= C) return;
-  for (int k = 1; k < 8; ++k) s += t[k][cx];
+  for (int k = 1; k < 32; ++k) s += t[k][cx];
   out[c] = s * scale;
 }
 
@@ -128,7 +130,7 @@ MTB_API int mtb_colsum_f32(const float* a, long long rows, int c, float scale, f
   if (cfg.vec == 4) colsum_partial_kernel<4><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   else colsum_partial_kernel<1><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
   MTB_LAUNCH_CHECK("colsum_partial_kernel");
-  colsum_final_kernel<<<mtb_div_up(c, 32), 256, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
+  colsum_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
   MTB_LAUNCH_CHECK("colsum_final_kernel");
   return MTB_OK;
 }
