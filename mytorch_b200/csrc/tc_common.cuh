@@ -162,7 +162,9 @@ __device__ __forceinline__ uint64_t smem_desc_mnmajor(uint32_t saddr, uint32_t l
 __host__ __device__ constexpr uint32_t desc_hi_kmajor() { return (1024u >> 4) | (1u << 14) | (2u << 29); }
 __host__ __device__ constexpr uint32_t desc_hi_mnmajor() { return (512u >> 4) | (1u << 14) | (1u << 29); }
 __device__ __forceinline__ uint32_t desc_lo_kmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | (1u << 16); }
-__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr) { return ((saddr >> 4) & 0x3FFFu) | ((4096u >> 4) << 16); }
+__device__ __forceinline__ uint32_t desc_lo_mnmajor(uint32_t saddr, uint32_t lbo_bytes = 4096u) {
+  return ((saddr >> 4) & 0x3FFFu) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
 
 __device__ __forceinline__ void mma_tf32_words(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
                                                uint32_t accumulate) {

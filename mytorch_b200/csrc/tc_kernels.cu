@@ -503,22 +503,35 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
 // kernel adds the partials in a fixed order and transposes into dW[co][tap][ci].
 namespace {
 
+// PB pixels (reduction elements) per stage; one A chunk = PB pixels x 32 channels.
+template <int BN, int PB>
+struct WCfg {
+  static constexpr uint32_t kChunk = PB * 128;
+  static constexpr uint32_t kABytes = 4 * kChunk;
+  static constexpr uint32_t kBBytes = (BN / 32) * kChunk;
+  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr int kStagesFit = (227 * 1024 - 2048) / kStageBytes;
+  static constexpr int kStages = kStagesFit > 6 ? 6 : kStagesFit;
+  static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr uint32_t kTmemCols = 2 * BN;
+};
+
 struct WgradParams {
   int Kw;            // KH*KW*Cin: rows of the transposed gradient
   int Cout;
   int chunks;        // Kw / 32
   int cchunks;       // Cin / 32
   int m_tiles, n_tiles, splits;
-  int kb_total;      // ceil(pixels / 32)
+  int kb_total;      // ceil(pixels / PB)
   int kb_per_split;
   int OW, OH, SW, SH, PW, PH, KW;
   float* partial;    // [splits][Kw][Cout]
 };
 
-template <int BN>
+template <int BN, int PB>
 __global__ void __launch_bounds__(192, 1)
 tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapDY, const WgradParams p) {
-  using C = Cfg<BN>;
+  using C = WCfg<BN, PB>;
   constexpr int STAGES = C::kStages;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_full[8], bar_empty[8], bar_tfull[2], bar_tempty[2];
@@ -565,7 +578,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
         const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
         int valid = p.chunks - m_tile * 4;
         if (valid > 4) valid = 4;
-        const uint32_t bytes = (uint32_t)valid * 4096u + C::kBBytes;
+        const uint32_t bytes = (uint32_t)valid * C::kChunk + C::kBBytes;
         int q_c[4], q_kw[4], q_kh[4];
         for (int q = 0; q < 4; ++q) {
           const int chunk = m_tile * 4 + (q < valid ? q : 0);
@@ -574,11 +587,11 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
           q_kh[q] = tap / p.KW;
           q_kw[q] = tap - q_kh[q] * p.KW;
         }
-        // first pixel of the range, then advanced by 32 pixels per block without divisions
-        int m = kb0 * 32;
+        // first pixel of the range, then advanced by PB pixels per block without divisions
+        int m = kb0 * PB;
         int ow = m % p.OW, tq = m / p.OW;
         int oh = tq % p.OH, pn_ = tq / p.OH;
-        for (int kb = kb0; kb < kb1; ++kb, m += 32) {
+        for (int kb = kb0; kb < kb1; ++kb, m += PB) {
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 11)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[stage]);
           mbar_expect_tx(full, bytes);
@@ -586,11 +599,11 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
           const int pw_ = ow * p.SW - p.PW, ph_ = oh * p.SH - p.PH;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            if (q < valid) tma_load_im2col_4d(a_dst + q * 4096, &mapX, full, q_c[q], pw_, ph_, pn_, (uint16_t)q_kw[q], (uint16_t)q_kh[q]);
+            if (q < valid) tma_load_im2col_4d(a_dst + q * C::kChunk, &mapX, full, q_c[q], pw_, ph_, pn_, (uint16_t)q_kw[q], (uint16_t)q_kh[q]);
 #pragma unroll
-          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapDY, full, n0 + 32 * j, m);
+          for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * C::kChunk, &mapDY, full, n0 + 32 * j, m);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-          ow += 32;
+          ow += PB;
           while (ow >= p.OW) {
             ow -= p.OW;
             if (++oh == p.OH) { oh = 0; ++pn_; }
@@ -603,7 +616,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       constexpr uint32_t idesc = idesc_tf32(128, BN, 1, 1);
       constexpr uint32_t hi = desc_hi_mnmajor();
       constexpr uint32_t step = 1024u >> 4;
-      const uint32_t a_lo0 = desc_lo_mnmajor(smem_base), b_lo0 = desc_lo_mnmajor(smem_base + C::kABytes);
+      const uint32_t a_lo0 = desc_lo_mnmajor(smem_base, C::kChunk), b_lo0 = desc_lo_mnmajor(smem_base + C::kABytes, C::kChunk);
       int stage = 0;
       uint32_t phase = 0;
       int t = 0;
@@ -623,9 +636,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
           tc_fence_after();
           const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
           mma_tf32_words(d_tmem, a_lo, hi, b_lo, hi, idesc, acc);
-          mma_tf32_words(d_tmem, a_lo + step, hi, b_lo + step, hi, idesc, 1u);
-          mma_tf32_words(d_tmem, a_lo + 2 * step, hi, b_lo + 2 * step, hi, idesc, 1u);
-          mma_tf32_words(d_tmem, a_lo + 3 * step, hi, b_lo + 3 * step, hi, idesc, 1u);
+#pragma unroll
+          for (int kk = 1; kk < PB / 8; ++kk) mma_tf32_words(d_tmem, a_lo + kk * step, hi, b_lo + kk * step, hi, idesc, 1u);
           acc = 1u;
           mma_commit(smem_u32(&bar_empty[stage]));
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -710,7 +722,7 @@ __global__ void __launch_bounds__(256) wgrad_reduce_transpose_kernel(const float
 }
 
 struct WgradPlan {
-  int bn, m_tiles, n_tiles, splits, kb_total, kb_per_split;
+  int bn, pb, m_tiles, n_tiles, splits, kb_total, kb_per_split;
   long long Kw, pixels;
 };
 
@@ -722,10 +734,14 @@ WgradPlan wgrad_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int s
   q.bn = pick_bn(cout);
   q.m_tiles = (int)((q.Kw + 127) / 128);
   q.n_tiles = (cout + q.bn - 1) / q.bn;
-  q.kb_total = (int)((q.pixels + 31) / 32);
+  // An im2col-mode load costs roughly the same whatever its size (measured: 4 loads of 32 pixels per
+  // stage ran at 100 TFLOP/s, 4 loads of 64 pixels at 169), so stages hold 64 pixels even where only
+  // two stages then fit (BN = 256: 239 -> 290 TFLOP/s).
+  q.pb = 64;
+  q.kb_total = (int)((q.pixels + q.pb - 1) / q.pb);
   const int tiles = q.m_tiles * q.n_tiles;
   int splits = (mtb_sm_count() + tiles - 1) / tiles;
-  const int max_splits = (q.kb_total + 7) / 8;  // at least 8 reduction blocks per CTA
+  const int max_splits = (q.kb_total + 3) / 4;  // at least 4 reduction blocks per CTA
   if (splits > max_splits) splits = max_splits;
   if (splits < 1) splits = 1;
   q.kb_per_split = (q.kb_total + splits - 1) / splits;
@@ -757,9 +773,9 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
   MTB_REQUIRE(workspace && workspace_bytes >= (long long)q.splits * q.Kw * cout * 4, "conv2d_wgrad: workspace too small");
   CUtensorMap mapX, mapDY;
-  int rc = tc::encode_im2col_4d(&mapX, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 32, true);
+  int rc = tc::encode_im2col_4d(&mapX, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, q.pb, true);
   if (rc) return rc;
-  rc = tc::encode_tiled_2d(&mapDY, dy, q.pixels, cout, cout, 32, 32, true);
+  rc = tc::encode_tiled_2d(&mapDY, dy, q.pixels, cout, cout, 32, q.pb, true);
   if (rc) return rc;
   WgradParams p{};
   p.Kw = (int)q.Kw; p.Cout = cout; p.chunks = (int)(q.Kw / 32); p.cchunks = cin / 32;
@@ -769,18 +785,19 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   cudaStream_t st = (cudaStream_t)stream;
   const int units = q.m_tiles * q.n_tiles * q.splits;
   const int grid = units < mtb_sm_count() ? units : mtb_sm_count();
-#define MTB_LAUNCH_WGRAD(BN_)                                                                                           \
+#define MTB_LAUNCH_WGRAD(BN_, PB_)                                                                                      \
   do {                                                                                                                  \
     static bool configured = false;                                                                                     \
     if (!configured) {                                                                                                  \
-      MTB_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel<BN_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg<BN_>::kSmemBytes)); \
+      MTB_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel<BN_, PB_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
+                                    (int)WCfg<BN_, PB_>::kSmemBytes));                                                  \
       configured = true;                                                                                                \
     }                                                                                                                   \
-    tc_wgrad_kernel<BN_><<<grid, 192, Cfg<BN_>::kSmemBytes, st>>>(mapX, mapDY, p);                                      \
+    tc_wgrad_kernel<BN_, PB_><<<grid, 192, WCfg<BN_, PB_>::kSmemBytes, st>>>(mapX, mapDY, p);                           \
   } while (0)
-  if (q.bn == 64) MTB_LAUNCH_WGRAD(64);
-  else if (q.bn == 128) MTB_LAUNCH_WGRAD(128);
-  else MTB_LAUNCH_WGRAD(256);
+  if (q.bn == 64) MTB_LAUNCH_WGRAD(64, 64);
+  else if (q.bn == 128) MTB_LAUNCH_WGRAD(128, 64);
+  else MTB_LAUNCH_WGRAD(256, 64);
 #undef MTB_LAUNCH_WGRAD
   MTB_LAUNCH_CHECK("tc_wgrad_kernel");
   dim3 rgrid((unsigned)((q.Kw + 31) / 32), (unsigned)((cout + 31) / 32));
