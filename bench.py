@@ -227,6 +227,14 @@ def run_gpu_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    trace_dir = os.environ.get("MTB_BENCH_TRACE")  # directory for per-rank progress logs (debugging aid)
+
+    def trace(msg):
+        if trace_dir:
+            with open(os.path.join(trace_dir, f"trace_rank{rank}.log"), "a") as f:
+                f.write(f"{time.time():.3f} {msg}\n")
+
+    trace("start")
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             sys.exit(f"--gpus {args.gpus} needs torchrun: python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...")
@@ -234,6 +242,7 @@ def run_gpu_arm(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
+        trace("process group up")
 
     import mytorch_b200 as mt
     import mytorch_b200.nn.functional as F
@@ -278,8 +287,12 @@ def run_gpu_arm(args):
             dist.barrier()
             torch.cuda.synchronize()
 
+    trace("model built")
     first_loss = step().item()
+    trace(f"first eager step done, loss {first_loss}")
     step()
+    torch.cuda.synchronize()
+    trace("second eager step done")
     runner = None
     if not args.no_graph:
         before = env.lib.launches
@@ -287,6 +300,7 @@ def run_gpu_arm(args):
         sg.capture()
         calls_per_step = env.lib.launches - before
         runner = sg
+        trace("graph captured")
     else:
         before = env.lib.launches
         step()
@@ -327,12 +341,15 @@ def run_gpu_arm(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
+    trace("warm-up done")
     total_ms = timed_region(lambda i: run_resident(), args.steps)
+    trace("timed region done")
     clocks = sampler.stop() if rank == 0 else None
     for i in range(2):
         run_e2e(i)
     e2e_ms = timed_region(run_e2e, args.steps)
     last_loss = run_e2e(0)
+    trace("e2e done")
 
     ms_per_step = total_ms / args.steps
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
@@ -378,8 +395,11 @@ def run_gpu_arm(args):
             "clocks": clocks, "roofline": roof, "kernels": kernels, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
+    trace("printed")
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
+    trace("exit")
 
 
 def main():
