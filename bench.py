@@ -397,8 +397,15 @@ def run_gpu_arm(args):
         print(json.dumps(line))
     trace("printed")
     if world > 1:
+        # Tearing down a NCCL process group whose collectives were captured in a CUDA graph that is
+        # still alive blocks in this PyTorch/NCCL combination; finish with a barrier and leave the
+        # process without running the communicator's destructor.
         dist.barrier()
-        dist.destroy_process_group()
+        torch.cuda.synchronize()
+        trace("exit")
+        sys.stdout.flush()
+        sys.stderr.flush()
+        os._exit(0)
     trace("exit")
 
 
