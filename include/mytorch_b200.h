@@ -107,6 +107,13 @@ int mtb_cast(int kind, const void* src, void* dst, long long n, void* stream);
  *      and ReduceTemplate, reduce_utils.cuh:24-62) ---- */
 long long mtb_colsum_workspace_bytes(int c);
 int mtb_colsum_f32(const float* a, long long rows, int c, float scale, float* out, void* workspace, long long workspace_bytes, void* stream);
+/* The same column sum for callers that can neither pass nor allocate scratch (an embedder whose arena
+ * owns all device memory, a step loop where driver allocations are off limits).  It has no counterpart
+ * in the reference.  Partials live in a 1 MiB device array inside the library; c <= 1024, otherwise
+ * MTB_ERR_UNSUPPORTED.  Performs no allocation.  The first call on each device resolves the array's
+ * address and should happen before any stream capture.  Calls share the array: do not let two of
+ * them overlap on one GPU. */
+int mtb_colsum_noalloc_f32(const float* a, long long rows, int c, float scale, float* out, void* stream);
 int mtb_nhwc_spatial_sum_f32(const float* x, float* y, int n, int c, int hw, float scale, void* stream);
 int mtb_nhwc_spatial_bcast_f32(const float* dy, float* dx, int n, int c, int hw, float scale, void* stream);
 int mtb_sum_strided_f32(const float* x, float* y, int nkept, const long long* kept_shape, const long long* kept_strides, int nred,

@@ -44,6 +44,7 @@ _SIGNATURES = {
     "mtb_add_relu_backward_f32": ([_P, _P, _P, _P, _L, _P], _I),
     "mtb_colsum_workspace_bytes": ([_I], _L),
     "mtb_colsum_f32": ([_P, _L, _I, _F, _P, _P, _L, _P], _I),
+    "mtb_colsum_noalloc_f32": ([_P, _L, _I, _F, _P, _P], _I),
     "mtb_nhwc_spatial_sum_f32": ([_P, _P, _I, _I, _I, _F, _P], _I),
     "mtb_nhwc_spatial_bcast_f32": ([_P, _P, _I, _I, _I, _F, _P], _I),
     "mtb_sum_strided_f32": ([_P, _P, _I, _P, _P, _I, _P, _P, _F, _P], _I),

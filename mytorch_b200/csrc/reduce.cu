@@ -169,3 +169,70 @@ MTB_API int mtb_sum_strided_f32(const float* x, float* y, int nkept, const long 
   MTB_LAUNCH_CHECK("strided_sum_kernel");
   return MTB_OK;
 }
+
+// ------------------------------------------------------------------ allocation-free variant
+//
+// Some callers cannot hand this library a scratch buffer and may not allocate one either: an
+// embedding runtime that gave all device memory to its own arena at start-up, or a step loop
+// in which any driver allocation is forbidden because it would synchronise the device.  For
+// them the column sum is also offered with its scratch inside the library image: a file-scope
+// device array of fixed size that every GPU loading the library carries until the process ends.
+namespace {
+
+constexpr int kNoAllocMaxChannels = 1024;
+constexpr int kNoAllocMaxPartials = 256;
+// 256 partial rows x 1024 channels x 4 bytes = 1 MiB per GPU.
+static __device__ __align__(256) float g_colsum_scratch[kNoAllocMaxPartials * kNoAllocMaxChannels];
+
+// In host code the name of a __device__ array is only a host-side stand-in; the device address
+// has to be asked for, once per device, with that device current.
+float* noalloc_scratch_for_current_device(int* status) {
+  static float* cached[64] = {nullptr};
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+    *status = mtb_fail(MTB_ERR_CUDA, "colsum_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (!cached[dev]) {
+    float* ptr = nullptr;
+    e = cudaGetSymbolAddress((void**)&ptr, g_colsum_scratch);
+    if (e != cudaSuccess || !ptr) {
+      *status = mtb_fail(MTB_ERR_CUDA, "colsum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = ptr;
+  }
+  *status = MTB_OK;
+  return cached[dev];
+}
+
+}  // namespace
+
+// out[c] = scale * sum_r a[r, c], like mtb_colsum_f32, but with no workspace argument and no
+// allocation of any kind: the per-CTA partial sums go to a 1 MiB array that is part of the
+// library.  Limits: c <= 1024 (more is rejected with MTB_ERR_UNSUPPORTED); at most 256 partial
+// rows are used, so very tall matrices run with fewer CTAs than mtb_colsum_f32 would use.
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
+// that first call before any stream capture begins.  All calls on a device share the one array
+// (it keeps the previous call's partials, every element that is read is rewritten first), so two
+// calls that may overlap on the GPU - different streams, no dependency - race with each other.
+MTB_API int mtb_colsum_noalloc_f32(const float* a, long long rows, int c, float scale, float* out, void* stream) {
+  MTB_REQUIRE(a && out && rows > 0 && c > 0, "colsum_noalloc: bad arguments");
+  if (c > kNoAllocMaxChannels)
+    return mtb_fail(MTB_ERR_UNSUPPORTED, "colsum_noalloc: %d channels exceed the built-in scratch (max %d); use mtb_colsum_f32 with a workspace",
+                    c, kNoAllocMaxChannels);
+  int status = MTB_OK;
+  float* partial = noalloc_scratch_for_current_device(&status);
+  if (!partial) return status;
+  cudaStream_t st = (cudaStream_t)stream;
+  ColCfg cfg = mtb_col_cfg(rows, c, mtb_aligned16(a), kNoAllocMaxPartials);
+  if (cfg.row_blocks > kNoAllocMaxPartials) return mtb_fail(MTB_ERR_UNSUPPORTED, "colsum_noalloc: internal partition exceeds the scratch");
+  dim3 grid(cfg.col_blocks, cfg.row_blocks);
+  if (cfg.vec == 4) colsum_partial_kernel<4><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+  else colsum_partial_kernel<1><<<grid, 256, 0, st>>>(a, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+  MTB_LAUNCH_CHECK("colsum_partial_kernel");
+  colsum_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, scale, out);
+  MTB_LAUNCH_CHECK("colsum_final_kernel");
+  return MTB_OK;
+}
