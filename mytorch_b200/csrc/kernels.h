@@ -30,3 +30,4 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
 bool mtb_tc_gemm_supported(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* c);
 int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu, float* c,
                     void* stream);
+

@@ -700,24 +700,31 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
 
 // dw[co][r] = sum_s partial[s][r][co]: 32x32 tiles, coalesced reads along co, smem transpose,
 // coalesced writes along r; splits added in index order.
-__global__ void __launch_bounds__(256) wgrad_reduce_transpose_kernel(const float* __restrict__ partial, float* __restrict__ dw, int Kw, int Cout,
-                                                                      int splits) {
+__global__ void __launch_bounds__(1024) wgrad_reduce_transpose_kernel(const float* __restrict__ partial, float* __restrict__ dw, int Kw, int Cout,
+                                                                       int splits) {
   __shared__ float tile[32][33];
   const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
   const long long plane = (long long)Kw * Cout;
-  for (int j = threadIdx.y; j < 32; j += 8) {
-    const int r = r0 + j, c = c0 + threadIdx.x;
-    float s = 0.f;
+  {
+    const int r = r0 + threadIdx.y, c = c0 + threadIdx.x;
+    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
     if (r < Kw && c < Cout) {
       const float* q = partial + (long long)r * Cout + c;
-      for (int z = 0; z < splits; ++z) s += q[z * plane];
+      int z = 0;
+      for (; z + 3 < splits; z += 4) {  // four independent loads in flight; the grouping is fixed
+        s0 += q[z * plane];
+        s1 += q[(z + 1) * plane];
+        s2 += q[(z + 2) * plane];
+        s3 += q[(z + 3) * plane];
+      }
+      for (; z < splits; ++z) s0 += q[z * plane];
     }
-    tile[j][threadIdx.x] = s;
+    tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
   }
   __syncthreads();
-  for (int j = threadIdx.y; j < 32; j += 8) {
-    const int c = c0 + j, r = r0 + threadIdx.x;
-    if (r < Kw && c < Cout) dw[(long long)c * Kw + r] = tile[threadIdx.x][j];
+  {
+    const int c = c0 + threadIdx.y, r = r0 + threadIdx.x;
+    if (r < Kw && c < Cout) dw[(long long)c * Kw + r] = tile[threadIdx.x][threadIdx.y];
   }
 }
 
@@ -801,7 +808,7 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
 #undef MTB_LAUNCH_WGRAD
   MTB_LAUNCH_CHECK("tc_wgrad_kernel");
   dim3 rgrid((unsigned)((q.Kw + 31) / 32), (unsigned)((cout + 31) / 32));
-  wgrad_reduce_transpose_kernel<<<rgrid, dim3(32, 8), 0, st>>>((const float*)workspace, dw, (int)q.Kw, cout, q.splits);
+  wgrad_reduce_transpose_kernel<<<rgrid, dim3(32, 32), 0, st>>>((const float*)workspace, dw, (int)q.Kw, cout, q.splits);
   MTB_LAUNCH_CHECK("wgrad_reduce_transpose_kernel");
   return MTB_OK;
 }
