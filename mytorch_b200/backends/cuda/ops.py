@@ -139,10 +139,43 @@ def _conv_args(x, w, stride, padding):
     return (n, cin, h, wd, kh, kw, stride[0], stride[1], padding[0], padding[1], cout)
 
 
+_TC_CHANNELS = 32  # the tensor-core convolution reads activations in blocks of 32 channels
+
+
+def _wants_channel_padding(x):
+    """Image stems (1 or 3 input channels) would otherwise run on the CUDA-core kernels; padding
+    their few channels with zeros up to one 32-channel block lets them use the tensor-core path
+    (extra zero FLOPs are far cheaper than the FFMA kernel) when the padded tensor is large enough
+    for that path to accept it."""
+    n, c, h, w = x.shape
+    return c < _TC_CHANNELS and n * h * w * _TC_CHANNELS * 4 >= (1 << 17)
+
+
+def _pad_channels(env, t, channels):
+    """Copy a channels-last tensor into a zero-filled one with `channels` channels (dim 1)."""
+    n, c, h, w = t.shape
+    out = _new((n, channels, h, w), t)
+    env.lib.fill_f32(_ptr(out), _numel(out.shape), 0.0, env.stream())
+    src = _strides(t)
+    env.lib.binary_strided_f32(5, 4, _ll(t.shape), _ll(src), _ll(src), _ll(_strides(out)), _ptr(t), None, _ptr(out), 1.0, env.stream())
+    return out
+
+
+def _take_channels(env, t, channels, like):
+    """First `channels` channels (dim 1) of a channels-last tensor, as a new tensor."""
+    n, c, h, w = t.shape
+    out = _new((n, channels, h, w), like)
+    src = _strides(t)
+    env.lib.binary_strided_f32(5, 4, _ll(out.shape), _ll(src), _ll(src), _ll(_strides(out)), _ptr(t), None, _ptr(out), 1.0, env.stream())
+    return out
+
+
 @_reg("cuda", "conv2d")
 def cuda_conv2d(input, weight, bias, stride, padding):
     _f32(input, weight, bias)
     env = _env(input)
+    if _wants_channel_padding(input):
+        input, weight = _pad_channels(env, input, _TC_CHANNELS), _pad_channels(env, weight, _TC_CHANNELS)
     a = _conv_args(input, weight, stride, padding)
     n, cin, h, w, kh, kw, sh, sw, ph, pw, cout = a
     oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
@@ -155,16 +188,24 @@ def cuda_conv2d(input, weight, bias, stride, padding):
 def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding):
     _f32(output_grad, input, weight)
     env = _env(input)
+    want_dx, want_dw, cin = input.requires_grad, weight.requires_grad, input.shape[1]
+    padded = _wants_channel_padding(input)
+    if padded:
+        input, weight = _pad_channels(env, input, _TC_CHANNELS), _pad_channels(env, weight, _TC_CHANNELS)
     a = _conv_args(input, weight, stride, padding)
     st = env.stream()
     ws, ws_bytes = env.workspace(env.lib.conv2d_workspace_bytes(*a))
     dx = dw = db = None
-    if input.requires_grad:
+    if want_dx:
         dx = _new(input.shape, input)
         env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(dx), ws, ws_bytes, st)
-    if weight.requires_grad:
+        if padded:
+            dx = _take_channels(env, dx, cin, dx)
+    if want_dw:
         dw = _new(weight.shape, weight)
         env.lib.conv2d_wgrad_f32(*a, _ptr(input), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)
+        if padded:
+            dw = _take_channels(env, dw, cin, dw)
     if bias is not None and bias.requires_grad:
         db = _colsum(env, output_grad, _numel(output_grad.shape) // a[-1], a[-1], bias)
     return [dx, dw, db]

@@ -337,7 +337,7 @@ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Activations smaller than this stay on the CUDA-core kernels: tiny tensors gain nothing from
 // the tensor cores, and im2col tensor maps over very small tensors are avoided altogether.
-constexpr long long kMinIm2colBytes = 256 * 1024;
+constexpr long long kMinIm2colBytes = 128 * 1024;
 
 }  // namespace
 
