@@ -211,12 +211,58 @@ def kernel_legs(torch, env, peaks):
     out["bn_bwd_gbs"] = 5 * S / t / 1e9
     t = timed(lambda i: op("relu")(sets[i % 3][0]))
     out["relu_fwd_gbs"] = 2 * S / t / 1e9
+    del sets, x, dy, res
+    # configs[1]: conv 64->64 3x3 on 128x56x56, forward + dgrad + wgrad (103 MB in, 103 MB out per pass)
+    n1 = 128
+    big = rng.standard_normal((n1, 64, 56, 56)).astype(np.float32)
+    c1 = [(mt.tensor(big, device="cuda", requires_grad=True), mt.tensor(big[::-1].copy(), device="cuda")) for _ in range(2)]
+    flops1 = 2.0 * n1 * 56 * 56 * 64 * 64 * 9
+    bias = mt.tensor(np.zeros(64, np.float32), device="cuda")
+    t_f = timed(lambda i: op("conv2d")(c1[i % 2][0], w, bias, (1, 1), (1, 1)))
+    w.requires_grad = False
+    t_d = timed(lambda i: op("conv2d_backward")(c1[i % 2][1], c1[i % 2][0], w, None, (1, 1), (1, 1)))
+    w.requires_grad = True
+    for xx, _ in c1:
+        xx.requires_grad = False
+    t_w = timed(lambda i: op("conv2d_backward")(c1[i % 2][1], c1[i % 2][0], w, None, (1, 1), (1, 1)))
+    out["config1_conv56_fwd_tflops"] = flops1 / t_f / 1e12
+    out["config1_conv56_dgrad_tflops"] = flops1 / t_d / 1e12
+    out["config1_conv56_wgrad_tflops"] = flops1 / t_w / 1e12
+    del c1
+    # configs[2]: BatchNorm2d(128) -> ReLU -> MaxPool2d(2,2) on 256x128x56x56 (S = 411 MB >> L2), forward and backward
+    big2 = (0.5 + 2.0 * rng.standard_normal((64, 128, 56, 56))).astype(np.float32)
+    x2 = mt.tensor(np.concatenate([big2] * 4, axis=0), device="cuda", requires_grad=True)
+    S2 = 4.0 * 256 * 128 * 56 * 56
+    g2 = mt.tensor(np.ones(128, np.float32), device="cuda", requires_grad=True)
+    b2 = mt.tensor(np.zeros(128, np.float32), device="cuda", requires_grad=True)
+    rm2, rv2 = mt.tensor(np.zeros(128, np.float32), device="cuda"), mt.tensor(np.ones(128, np.float32), device="cuda")
+    r2 = {}
+
+    def bn2_f(i):
+        r2["y"], r2["m"], r2["v"] = op("batch_norm2d")(x2, g2, b2, 1e-5, True, 0.1, rm2, rv2)
+
+    out["config2_bn_fwd_gbs"] = 3 * S2 / timed(bn2_f, reps=5) / 1e9
+    out["config2_bn_bwd_gbs"] = 5 * S2 / timed(lambda i: op("batch_norm2d_backward")(r2["y"], r2["m"], r2["v"], x2, g2, b2, 1e-5), reps=5) / 1e9
+    out["config2_relu_fwd_gbs"] = 2 * S2 / timed(lambda i: r2.__setitem__("r", op("relu")(r2["y"])), reps=5) / 1e9
+    out["config2_relu_bwd_gbs"] = 3 * S2 / timed(lambda i: op("relu_backward")(x2, r2["y"]), reps=5) / 1e9
+
+    def pool_f(i):
+        r2["p"] = op("max_pool2d")(r2["r"], (2, 2), (2, 2), (0, 0))
+
+    # forward: read S, write S/4 values + S/8 tie mask (uint16 per output); backward: read S/4 + S/8, write S
+    out["config2_maxpool_fwd_gbs"] = 1.375 * S2 / timed(pool_f, reps=5) / 1e9
+    dyp = mt.tensor(big2[:, :, ::2, ::2].repeat(4, axis=0).copy(), device="cuda")
+    out["config2_maxpool_bwd_gbs"] = 1.375 * S2 / timed(lambda i: op("max_pool2d_backward")(dyp, r2["p"], r2["r"], (2, 2), (2, 2), (0, 0)), reps=5) / 1e9
+    del r2, x2, dyp
     roof = {"bound": "tensor", "kernel": "conv2d forward 64->64 3x3 s1 p1 on 512x32x32 (dominant layer shape of the step)",
             "achieved": out["conv3x3_64_fwd_tflops"], "peak": tf32_peak, "unit": "TFLOP/s", "frac": out["conv3x3_64_fwd_tflops"] / tf32_peak,
-            "traffic": None,
+            # dram__bytes_read.sum + dram__bytes_write.sum of one launch of this kernel and shape, from the ncu
+            # capture summarised in profiles/ (134.5 MB read + 86.4 MB written; algorithmic: 134 + 134 MB)
+            "traffic": 220.9e6, "algorithmic_flops_per_launch": flops,
             "peak_note": f"TF32 dense = half of the {peaks['source']} bf16 burst figure ({peaks['bf16_tflops']} TFLOP/s); "
                          f"HBM figures in `kernels` are against {peaks['hbm_gbs']} GB/s ({peaks['source']})"}
-    out["hbm_frac"] = {k: out[k] / peaks["hbm_gbs"] for k in ("bn_fwd_gbs", "bn_bwd_gbs", "relu_fwd_gbs")}
+    out["hbm_frac"] = {k: out[k] / peaks["hbm_gbs"] for k in out if k.endswith("_gbs")}
+    out["tf32_frac"] = {k: out[k] / tf32_peak for k in out if k.endswith("_tflops")}
     return roof, out
 
 

@@ -264,3 +264,30 @@ def test_fused_and_unfused_models_agree_bitwise():
     assert la == lb
     for a, b in zip(pa, pb):
         assert np.array_equal(a, b)
+
+
+def test_resnet50_and_small_cnn_train_steps_run_and_learn():
+    """The ImageNet-shaped ResNet-50 (7x7/2 stem, 3x3/2 max-pool with padding, bottlenecks) and the
+    MNIST-shaped CNN both take optimisation steps that reduce the loss on a fixed batch."""
+    import gpu_util as g
+    import mytorch_b200 as mt
+    import mytorch_b200.nn.functional as F
+    from mytorch_b200.examples.models import ResNet50, small_cnn
+    from mytorch_b200.optim import SGD
+
+    rng = np.random.default_rng(50)
+    for build, shape, classes, lr in [(lambda: ResNet50(num_classes=16), (4, 3, 64, 64), 16, 0.02), (small_cnn, (32, 1, 28, 28), 10, 0.05)]:
+        mt.manual_seed(4)
+        net = build()
+        net.to(g.DEV)
+        opt = SGD(net.parameters(), lr=lr, momentum=0.9)
+        x = g.dev(rng.standard_normal(shape).astype(np.float32))
+        t = g.dev(rng.integers(0, classes, shape[0]).astype(np.int64))
+        losses = []
+        for _ in range(6):
+            loss = F.cross_entropy(net(x), t)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            losses.append(loss.item())
+        assert all(np.isfinite(losses)) and losses[-1] < losses[0], losses
