@@ -18,6 +18,7 @@ from oracle import models as OM
 pytestmark = pytest.mark.gpu
 
 TOL = 5e-3
+LATER_TOL = 3e-2
 GRAD_TOL = 0.15    # whole gradient / parameter vector, relative L2
 TENSOR_TOL = 0.5   # any single tensor (a 16-element BatchNorm gradient moves a lot when one ReLU mask flips)
 
@@ -61,7 +62,10 @@ def _train(net, x, t, lr, momentum, steps, gd, tag, tol=GRAD_TOL):
         if s == 0:
             _check_summary(gd, f"{tag}/param{s}", [(k, g.host(v.detach())) for k, v in net.named_parameters()], tol)
         losses.append(loss.item())
-        assert abs(losses[-1] - gd[f"{tag}/losses"][s]) < TOL * abs(gd[f"{tag}/losses"][s])
+        # the first loss depends on the forward pass alone; later ones on parameters updated with
+        # TF32 gradients of a tiny, badly conditioned net (batch 8, widths 8..64), hence LATER_TOL
+        ref_loss = gd[f"{tag}/losses"][s]
+        assert abs(losses[-1] - ref_loss) < (TOL if s == 0 else LATER_TOL) * abs(ref_loss), (s, losses[-1], ref_loss)
     if steps == 1:
         _check_summary(gd, f"{tag}/buffers", [(k, g.host(v)) for k, v in net.named_buffers()], tol)
     return losses
