@@ -12,18 +12,19 @@ struct PoolDims {
   int N, C, H, W, KH, KW, SH, SW, PH, PW, OH, OW;
 };
 
-template <int V>
+// IdxT = unsigned when the element count fits 32 bits (cheap div/mod), long long otherwise.
+template <int V, typename IdxT>
 __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restrict__ x, float* __restrict__ y, unsigned short* __restrict__ mask,
-                                                           PoolDims d, long long total) {
-  const int cv = d.C / V;
-  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
-  long long stride = (long long)gridDim.x * blockDim.x;
+                                                           PoolDims d, long long total_ll) {
+  const IdxT cv = (IdxT)(d.C / V), total = (IdxT)total_ll;
+  IdxT i = (IdxT)blockIdx.x * blockDim.x + threadIdx.x;
+  const IdxT stride = (IdxT)gridDim.x * blockDim.x;
   for (; i < total; i += stride) {
     int cg = (int)(i % cv);
-    long long t = i / cv;
-    int ow = (int)(t % d.OW); t /= d.OW;
-    int oh = (int)(t % d.OH);
-    int n = (int)(t / d.OH);
+    IdxT t = i / cv;
+    int ow = (int)(t % (IdxT)d.OW); t /= (IdxT)d.OW;
+    int oh = (int)(t % (IdxT)d.OH);
+    int n = (int)(t / (IdxT)d.OH);
     float best[V];
     unsigned m[V];
 #pragma unroll
@@ -47,14 +48,18 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
         }
       }
     }
-    long long o = i * V;
+    long long o = (long long)i * V;
     VecF<V> r;
 #pragma unroll
     for (int k = 0; k < V; ++k) r.v[k] = best[k];
     vstore<V>(y + o, r);
     if (mask) {
+      if (V == 4) {
+        *reinterpret_cast<uint2*>(mask + o) = make_uint2(m[0] | (m[1 % V] << 16), m[2 % V] | (m[3 % V] << 16));
+      } else {
 #pragma unroll
-      for (int k = 0; k < V; ++k) mask[o + k] = (unsigned short)m[k];
+        for (int k = 0; k < V; ++k) mask[o + k] = (unsigned short)m[k];
+      }
     }
   }
 }
@@ -106,6 +111,32 @@ __global__ void __launch_bounds__(256) maxpool_bwd_kernel(const float* __restric
   }
 }
 
+// Non-overlapping windows that tile the input exactly (kernel == stride, no padding, extents
+// divisible): one thread per output window and 4 channels reads dy and the tie mask once and
+// writes the KH*KW input gradients of its window, so nothing is read twice.
+__global__ void __launch_bounds__(256) maxpool_bwd_window_kernel(const float* __restrict__ dy, const unsigned short* __restrict__ mask,
+                                                                  float* __restrict__ dx, PoolDims d, unsigned total) {
+  const unsigned cv = d.C / 4;
+  unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (; i < total; i += stride) {
+    unsigned cg = i % cv, t = i / cv;
+    unsigned ow = t % d.OW; t /= d.OW;
+    unsigned oh = t % d.OH, n = t / d.OH;
+    const long long o = (long long)i * 4;
+    const float4 g = ld4(dy + o);
+    const uint2 mm = *reinterpret_cast<const uint2*>(mask + o);
+    const unsigned m0 = mm.x & 0xffffu, m1 = mm.x >> 16, m2 = mm.y & 0xffffu, m3 = mm.y >> 16;
+    for (int kh = 0; kh < d.KH; ++kh) {
+      float* row = dx + ((((long long)n * d.H + oh * d.KH + kh) * d.W + (long long)ow * d.KW) * d.C) + cg * 4;
+      for (int kw = 0; kw < d.KW; ++kw) {
+        const unsigned bit = 1u << (kh * d.KW + kw);
+        st4(row + (long long)kw * d.C, make_float4((m0 & bit) ? g.x : 0.f, (m1 & bit) ? g.y : 0.f, (m2 & bit) ? g.z : 0.f, (m3 & bit) ? g.w : 0.f));
+      }
+    }
+  }
+}
+
 __global__ void mask_to_argmax_kernel(const unsigned short* __restrict__ mask, unsigned char* __restrict__ argmax, long long n) {
   long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   long long stride = (long long)gridDim.x * blockDim.x;
@@ -130,11 +161,15 @@ MTB_API int mtb_max_pool2d_forward_f32(int n, int c, int h, int w, int kh, int k
   if (rc) return rc;
   MTB_REQUIRE(x && y, "max_pool2d_forward: null pointer");
   MTB_REQUIRE(!tiemask || kh * kw <= 16, "max_pool2d_forward: tie mask needs KH*KW <= 16");
-  bool vec = c % 4 == 0 && mtb_aligned16(x) && mtb_aligned16(y);
+  bool vec = c % 4 == 0 && mtb_aligned16(x) && mtb_aligned16(y) && (reinterpret_cast<uintptr_t>(tiemask) & 7u) == 0;
   long long total = (long long)n * d.OH * d.OW * (c / (vec ? 4 : 1));
   int grid = mtb_stream_grid(total, 256);
-  if (vec) maxpool_fwd_kernel<4><<<grid, 256, 0, (cudaStream_t)stream>>>(x, y, tiemask, d, total);
-  else maxpool_fwd_kernel<1><<<grid, 256, 0, (cudaStream_t)stream>>>(x, y, tiemask, d, total);
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool small = total < (1LL << 31) - (1LL << 26);  // room for the grid-stride overshoot
+  if (vec && small) maxpool_fwd_kernel<4, unsigned><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
+  else if (vec) maxpool_fwd_kernel<4, long long><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
+  else if (small) maxpool_fwd_kernel<1, unsigned><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
+  else maxpool_fwd_kernel<1, long long><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
   MTB_LAUNCH_CHECK("maxpool_fwd_kernel");
   return MTB_OK;
 }
@@ -152,7 +187,12 @@ MTB_API int mtb_max_pool2d_backward_f32(int n, int c, int h, int w, int kh, int 
   long long total = (long long)n * h * w * (c / (vec ? 4 : 1));
   int grid = mtb_stream_grid(total, 256);
   cudaStream_t st = (cudaStream_t)stream;
-  if (tiemask) {
+  const bool tiles_exactly = kh == sh && kw == sw && ph == 0 && pw == 0 && h % kh == 0 && w % kw == 0;
+  if (tiemask && vec && tiles_exactly && (long long)n * d.OH * d.OW * (c / 4) < (1LL << 31) &&
+      (reinterpret_cast<uintptr_t>(tiemask) & 7u) == 0) {
+    const unsigned windows = (unsigned)((long long)n * d.OH * d.OW * (c / 4));
+    maxpool_bwd_window_kernel<<<mtb_stream_grid(windows, 256), 256, 0, st>>>(dy, tiemask, dx, d, windows);
+  } else if (tiemask) {
     if (vec) maxpool_bwd_kernel<4, 0><<<grid, 256, 0, st>>>(dy, tiemask, out, x, dx, d, total);
     else maxpool_bwd_kernel<1, 0><<<grid, 256, 0, st>>>(dy, tiemask, out, x, dx, d, total);
   } else {
