@@ -19,7 +19,7 @@ struct ColCfg {
   long long rows_per_block;
 };
 
-static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_row_blocks = 0) {
+static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_row_blocks = 0, int ctas_per_sm = 4) {
   ColCfg c;
   c.vec = (aligned && C % 4 == 0) ? 4 : 1;
   c.cv = C / c.vec;
@@ -28,7 +28,7 @@ static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_ro
   c.lanes = lanes;
   c.rows_per_iter = 256 / lanes;
   c.col_blocks = (c.cv + lanes - 1) / lanes;
-  long long target = (long long)mtb_sm_count() * 4 / c.col_blocks;
+  long long target = (long long)mtb_sm_count() * ctas_per_sm / c.col_blocks;
   if (target < 1) target = 1;
   if (max_row_blocks > 0 && target > max_row_blocks) target = max_row_blocks;
   long long min_rows = (long long)c.rows_per_iter * 32;  // at least 32 loop trips per thread
@@ -45,7 +45,7 @@ static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_ro
 }
 
 // Upper bound on row_blocks for any shape (used to size scratch).
-static inline int mtb_col_max_partials() { return mtb_sm_count() * 4; }
+static inline int mtb_col_max_partials() { return mtb_sm_count() * 6; }
 
 template <int V> struct VecF { float v[V]; };
 

@@ -224,8 +224,9 @@ def test_step_is_bitwise_reproducible_and_graph_replay_matches_eager():
         if use_graph:
             sg = StepGraph(step, [xt, tt])
             sg.capture()                      # capture executes nothing; it records step 3
-            for _ in range(2):
-                losses.append(sg.replay([x, t]).item())
+            losses.append(sg.replay([x, t]).item())          # blocking refill of the static inputs
+            sg.prefetch([x, t])                                # double-buffered refill on a side stream
+            losses.append(sg.replay(prefetched=True).item())
         else:
             losses += [step().item(), step().item()]
         return losses, [g.host(p.detach()) for p in net.parameters()]
