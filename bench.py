@@ -461,17 +461,21 @@ def run_gpu_arm(args):
 
 
 def main():
+    global GLOBAL_BATCH
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
+    ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
+                    help="profiling aid: run the step at another global batch (the benchmark configuration is 512)")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
     ap.add_argument("--only-legs", action="store_true",
                     help="run only the single-kernel legs (conv fwd/dgrad/wgrad, BatchNorm, ReLU) and print their JSON; "
                          "this is the command profiled with ncu for the summaries under profiles/")
     args = ap.parse_args()
+    GLOBAL_BATCH = args.global_batch
     if args.only_legs:
         import torch
 

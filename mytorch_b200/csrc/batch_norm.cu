@@ -33,7 +33,7 @@ __global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __re
       cnt = 1;
       r += R;
     }
-#pragma unroll 8
+#pragma unroll 4
     for (; r < r1; r += R) {
       VecF<V> f = vload<V>(x + r * C + (long long)cg * V);
 #pragma unroll
@@ -345,7 +345,7 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
   float* scale = partial + (long long)mtb_col_max_partials() * 3 * c;
   int fin_blocks = mtb_div_up(c, 128);
   if (training) {
-    ColCfg cfg = mtb_col_cfg(rows, c, aligned, 0, 6);  // 6 CTAs of 256 threads are resident per SM
+    ColCfg cfg = mtb_col_cfg(rows, c, aligned);
     dim3 grid(cfg.col_blocks, cfg.row_blocks);
     if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);

@@ -31,7 +31,7 @@ static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_ro
   long long target = (long long)mtb_sm_count() * ctas_per_sm / c.col_blocks;
   if (target < 1) target = 1;
   if (max_row_blocks > 0 && target > max_row_blocks) target = max_row_blocks;
-  long long min_rows = (long long)c.rows_per_iter * 32;  // at least 32 loop trips per thread
+  long long min_rows = (long long)c.rows_per_iter * 8;  // at least 8 loop trips per thread
   long long want = (rows + min_rows - 1) / min_rows;
   if (want < 1) want = 1;
   c.row_blocks = (int)(want < target ? want : target);
@@ -45,7 +45,7 @@ static inline ColCfg mtb_col_cfg(long long rows, int C, bool aligned, int max_ro
 }
 
 // Upper bound on row_blocks for any shape (used to size scratch).
-static inline int mtb_col_max_partials() { return mtb_sm_count() * 6; }
+static inline int mtb_col_max_partials() { return mtb_sm_count() * 4; }
 
 template <int V> struct VecF { float v[V]; };
 

@@ -333,6 +333,17 @@ int launch_tc_bn(int bn, const CUtensorMap& mapA, const CUtensorMap& mapB, const
 
 int pick_bn(int n) { return n <= 64 ? 64 : (n <= 128 ? 128 : 256); }
 
+// Tile width for a GEMM with `rows` output rows: the widest tile (best MMA efficiency) that still
+// yields enough tiles to occupy most SMs; small problems (late layers at small batch) fall back
+// to narrower tiles so that more CTAs take part.
+int pick_bn_for(int n, long long rows) {
+  const long long m_tiles = (rows + 127) / 128;
+  const int want = mtb_sm_count() * 3 / 4;
+  int bn = pick_bn(n);
+  while (bn > 64 && m_tiles * ((n + bn - 1) / bn) < want) bn >>= 1;
+  return bn;
+}
+
 bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Activations smaller than this stay on the CUDA-core kernels: tiny tensors gain nothing from
@@ -370,7 +381,7 @@ bool mtb_tc_gemm_supported(int m, int n, int k, const float* a, int trans_a, con
 int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu, float* c,
                     void* stream) {
   CUtensorMap mapA, mapB;
-  int bn = pick_bn(n);
+  int bn = pick_bn_for(n, m);
   int rc;
   if (!trans_a) rc = tc::encode_tiled_2d(&mapA, a, m, k, k, 32, 128);
   else rc = tc::encode_tiled_2d(&mapA, a, k, m, m, 32, 32, true);
@@ -404,7 +415,7 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
                               const float* wt, const float* bias, float* y, int relu, void* stream) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   const long long M = (long long)n * oh * ow, K = (long long)kh * kw * cin;
-  const int bn = pick_bn(cout);
+  const int bn = pick_bn_for(cout, M);
   CUtensorMap mapA, mapB;
   int rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
   if (rc) return rc;
@@ -441,7 +452,7 @@ bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw,
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                             const float* wt, float* dx, void*, long long, void* stream) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
-  const int bn = pick_bn(cin);
+  const int bn = pick_bn_for(cin, (long long)n * h * w / (sh * sw));
   cudaStream_t st = (cudaStream_t)stream;
   CUtensorMap mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32, true);

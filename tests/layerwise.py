@@ -92,9 +92,15 @@ class LayerwiseChecker:
                 c = x.shape[1]
                 hm, hv, hx, hdy = _h(mean).reshape(1, c, 1, 1), _h(var).reshape(1, c, 1, 1), _h(x.detach()), _h(dy)
                 if name.endswith("relu"):
-                    # the reference would run relu_backward on the BatchNorm output first; the mask is
-                    # taken from the forward output recorded for this node (y > 0)
-                    hdy = np.where(self._fused_out[id(x)] > 0, hdy, 0).astype(hdy.dtype)
+                    # the reference would run relu_backward on the BatchNorm output first, which blocks
+                    # the gradient only where that output is negative.  The mask is taken from the
+                    # forward output recorded for this node (y > 0), plus the elements whose
+                    # normalised value is exactly zero (x equal to the batch mean with beta = 0):
+                    # their forward output is 0 as well, but the gradient passes.
+                    hg, hb = _h(gam.detach()).reshape(1, c, 1, 1), _h(b.detach()).reshape(1, c, 1, 1)
+                    pre = (hx - hm) * (hg / np.sqrt(hv + np.float32(eps), dtype=np.float32)) + hb
+                    keep = (self._fused_out[id(x)] > 0) | (pre == 0)
+                    hdy = np.where(keep, hdy, 0).astype(hdy.dtype)
                 rdx, rdg, rdb = O.batch_norm2d_backward(hdy, hm, hv, hx, _h(gam.detach()), eps)
                 self._note("bwd", name + ".dx", g[0], rdx, FP32_TOL * 2)
                 self._note("bwd", name + ".dgamma", g[1], rdg, FP32_TOL * 3)
