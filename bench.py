@@ -314,7 +314,7 @@ def run_gpu_arm(args):
     mt.manual_seed(SEED)
     net = ResNet18Cifar()
     net.to(dev)
-    dp = DataParallel(net)
+    dp = DataParallel(net, buckets=args.grad_buckets)
     opt = SGD(net.parameters(), lr=0.1, momentum=0.9)
     xs = mt.tensor(x_all[lo:hi], device=dev)
     ts = mt.tensor(t_all[lo:hi], device=dev)
@@ -434,7 +434,7 @@ def run_gpu_arm(args):
             "metric": "train_images_per_sec", "value": value, "unit": "images/s", "n_gpus": world, "steps": args.steps,
             "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "tf32 (fp32 storage, fp32 accumulate)", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_batch, "parallelism": f"dp{world}",
+            "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "per_gpu_batch": local_batch, "parallelism": f"dp{world}", "grad_buckets": args.grad_buckets if world > 1 else None,
                        "cuda_graph": not args.no_graph,
                        "l2": "no flush: one step streams ~1.3 GB of activations per pass, 10x the 126 MB L2"},
             "step_tflops": step_flops / (ms_per_step * 1e-3) / 1e12,
@@ -470,6 +470,9 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="profiling aid: run the step at another global batch (the benchmark configuration is 512)")
+    ap.add_argument("--grad-buckets", type=int, default=2,
+                    help="gradient all-reduce buckets (N>1): 1 = one all-reduce after backward, more = start each "
+                         "bucket on a side stream as soon as backward has finished its gradients")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
     ap.add_argument("--only-legs", action="store_true",
                     help="run only the single-kernel legs (conv fwd/dgrad/wgrad, BatchNorm, ReLU) and print their JSON; "

@@ -36,6 +36,9 @@ class DAGTracker:
         self._backward_funcs = {}
         self._seq = 0
         self.no_grad = False
+        # optional callback(tensor): a leaf tensor has received its last gradient contribution of
+        # the running backward pass (used to start gradient all-reduces while backward continues)
+        self.leaf_grad_final_hook = None
 
     def register_backward_function(self, op_name):
         def decorator(func):
@@ -78,18 +81,32 @@ class DAGTracker:
         seed.fill_(1)
         tensor.grad = seed
 
+        hook = self.leaf_grad_final_hook
+        pending = {}
+        if hook is not None:  # how many contributions every leaf will receive
+            for node in order:
+                for arg in node.inputs:
+                    if isinstance(arg, Tensor) and arg.requires_grad and arg._grad_node is None:
+                        pending[id(arg)] = pending.get(id(arg), 0) + 1
+
         for node in order:
             func = self._backward_funcs[node.name]
-            grads = func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs)
+            grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs))
+            grads += [None] * (len(node.inputs) - len(grads))
             for arg, grad in zip(node.inputs, grads):
-                if arg is None or not isinstance(arg, Tensor) or not arg.requires_grad or grad is None:
+                if arg is None or not isinstance(arg, Tensor) or not arg.requires_grad:
                     continue
-                if arg.grad is None:
-                    arg.grad = grad
-                else:
-                    if arg.grad.shape != grad.shape:
-                        raise MismatchShapesError([arg.grad.shape, grad.shape])
-                    arg.grad = arg.grad + grad
+                if grad is not None:
+                    if arg.grad is None:
+                        arg.grad = grad
+                    else:
+                        if arg.grad.shape != grad.shape:
+                            raise MismatchShapesError([arg.grad.shape, grad.shape])
+                        arg.grad = arg.grad + grad
+                if hook is not None and id(arg) in pending:
+                    pending[id(arg)] -= 1
+                    if pending[id(arg)] == 0 and arg.grad is not None:
+                        hook(arg)
 
         for node in order:
             for t in node.outputs:

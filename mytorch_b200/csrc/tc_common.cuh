@@ -71,6 +71,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
                : "memory");
 }
+// tiled mode over a channels-last tensor {C, W, H, N}; coordinates outside the tensor read zeros
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c, int w, int h, int n) {
+  asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+               ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
+               : "memory");
+}
 // im2col mode over a channels-last tensor {C, W, H, N}: c/w/h/n locate the first pixel (in
 // input coordinates, i.e. already multiplied by the stride and shifted by -padding); off_w/off_h
 // are the filter-tap offsets.
@@ -83,6 +89,14 @@ __device__ __forceinline__ void tma_load_im2col_4d(uint32_t dst, const CUtensorM
 }
 __device__ __forceinline__ void prefetch_tensormap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// One lane of a converged warp (the others skip the guarded block); the warp stays converged, so
+// values computed before the block from warp-uniform inputs can live in uniform registers.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(pred));
+  return pred != 0;
 }
 
 // ---- tcgen05 ----
@@ -192,6 +206,9 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, int a_mn_major, 
 // mn_major selects the 32-byte-atom swizzle that MN-major tcgen05 operands need.
 int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long long cols, long long pitch_elems, int box_cols, int box_rows,
                     bool mn_major = false);
+// channels-last activation {C, W, H, N}; a load takes `box_w` consecutive pixels of one image
+// row x `channels` channels (tiled mode, 128-byte swizzle, zero fill outside the tensor).
+int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w);
 // channels-last activation {C, W, H, N}; a load takes `pixels` output pixels x `channels`
 // channels for one filter tap of a convolution with the given stride / lower padding; `upper`
 // = lower_pad - (filter - 1) per spatial dim bounds the walk of the window origin.

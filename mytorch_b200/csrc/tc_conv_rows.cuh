@@ -1,0 +1,413 @@
+// Stride-1 "same" convolution (KH = 2*PH+1, KW = 2*PW+1) on tcgen05 with the activation staged
+// ONCE per tile instead of once per filter tap.
+//
+// The im2col-mode kernel copies every input pixel into shared memory KH*KW times (once per
+// tap).  Shared memory moves 128 B per cycle per SM in total, shared between the copy engine
+// writing tiles and the tensor core reading them, and for narrow layers that traffic, not the
+// MMA rate, bounds the kernel.  Here the activation is laid out in shared memory as whole image
+// rows, each padded to Wp = W + 2*PW pixels with the zeros the copy engine fills in beyond the
+// edges; consecutive rows follow each other without gaps, and images are separated by PH rows
+// of zeros.  In that "padded linear" space the pixel a tap (kh, kw) needs for output position q
+// is simply position q + (kh-PH)*Wp + (kw-PW), so the A operand of every tap is the SAME
+// shared-memory tile read through a descriptor whose start address is shifted by whole
+// 128-byte rows (the 128-byte swizzle is a function of the address bits, so a row shift keeps
+// it consistent).  A tile is 128 consecutive positions; positions that fall on padding columns
+// or separator rows are computed and thrown away (W*H / (Wp*(H+PH)) of the work is useful,
+// 91 % for 32x32 images and 3x3 filters).
+//
+// Loop nest per tile: for each block of 32 reduction channels { stage the rows once (one copy
+// per image row); for each tap { stage the BN x 32 weight tile; 4 MMAs of K = 8 } }.
+// Roles, barriers, bounded waits and the TMEM double buffer are those of tc_gemm_kernel.
+#pragma once
+
+namespace {
+using namespace tc;
+
+struct RowConvParams {
+  long long Q;             // positions: N * Hv * Wp
+  int Wp, Hv, H, W, PH, PW, KH, KW;
+  int cchunks;             // reduction channels / 32
+  int kc_total;            // reduction channels (pitch of one tap in the K-major weight matrix)
+  int N;                   // output channels
+  int m_tiles, n_tiles;
+  uint32_t a_stage_bytes;  // multiple of 1024; rows start kRowLead bytes into the stage
+  int b_stages;            // weight ring depth
+  int tps;                 // filter taps per weight stage
+  int resident;            // the whole filter (all taps, all channel blocks) stays in shared memory
+  float* out;
+  long long ldo;
+  const float* bias;
+  int relu;
+  int b_tap_x[64];         // MN-major B only: first column of tap j in the weight matrix
+};
+
+constexpr uint32_t kRowLead = 1024;  // room for the left-most tap of the first position to reach back
+constexpr int kRowAStages = 2;
+
+// Why a weight stage holds several taps: one producer/consumer hand-over through a pair of
+// mbarriers costs the issuing thread about 300-400 cycles that do not overlap with tensor-core
+// work, and a tcgen05.mma takes ~45 cycles to issue whatever its width, so a stage of 4 narrow
+// MMAs (192 cycles of work at N = 64) leaves the tensor core idle most of the time.  With all
+// nine taps of a 3x3 filter in one stage (36 MMAs) the hand-over is amortised.
+template <int BN, int BMODE, int FK>
+__global__ void __launch_bounds__(192, 1)
+tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const RowConvParams p) {
+  constexpr uint32_t kTapBytes = BN * 128;
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_afull[kRowAStages], bar_aempty[kRowAStages], bar_bfull[8], bar_bempty[8], bar_tfull[2], bar_tempty[2], bar_bres;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t b_base = smem_base + kRowAStages * p.a_stage_bytes;
+  const uint32_t b_stage_bytes = (uint32_t)p.tps * kTapBytes;
+  const int BST = p.b_stages;
+
+  // The shifted reads of the first and last positions of a tile reach a few rows outside what
+  // the copies of that tile wrote; those rows only feed discarded outputs, but they must hold
+  // finite numbers for nothing else, so the lead and the tail of every stage start as zeros.
+  for (uint32_t i = threadIdx.x; i < kRowAStages * p.a_stage_bytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(smem_raw + (smem_base - smem_u32(smem_raw)))[i] = make_uint4(0, 0, 0, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kRowAStages; ++s) {
+      mbar_init(smem_u32(&bar_afull[s]), 1);
+      mbar_init(smem_u32(&bar_aempty[s]), 1);
+    }
+    for (int s = 0; s < 8; ++s) {
+      mbar_init(smem_u32(&bar_bfull[s]), 1);
+      mbar_init(smem_u32(&bar_bempty[s]), 1);
+    }
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(smem_u32(&bar_tfull[b]), 1);
+      mbar_init(smem_u32(&bar_tempty[b]), 4);  // one arrival per epilogue warp
+    }
+    mbar_init(smem_u32(&bar_bres), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 2 * BN);
+    tmem_relinquish();
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int taps = p.KH * p.KW;
+  volatile int* abort_ptr = &abort_flag;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&mapA);
+      prefetch_tensormap(&mapB);
+      int as = 0, bs = 0;
+      uint32_t aphase = 0, bphase = 0;
+      bool ok = true;
+      const uint32_t row_bytes = (uint32_t)p.Wp * 128u;
+      if (p.resident && blockIdx.x < tiles) {
+        // one output-channel tile in all: every (channel block, tap) weight tile is fetched once
+        const uint32_t bres = smem_u32(&bar_bres);
+        mbar_expect_tx(bres, (uint32_t)(p.cchunks * taps) * kTapBytes);
+        uint32_t b_dst = b_base;
+        for (int cc = 0; cc < p.cchunks; ++cc)
+          for (int tap = 0; tap < taps; ++tap, b_dst += kTapBytes) {
+            if (BMODE == B_KMAJOR) {
+              tma_load_2d(b_dst, &mapB, bres, tap * p.kc_total + cc * 32, 0);
+            } else {
+#pragma unroll
+              for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, bres, p.b_tap_x[tap] + 32 * j, cc * 32);
+            }
+          }
+      }
+      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+        const long long q0 = (long long)(tile / p.n_tiles) * 128;
+        const int n0 = (tile % p.n_tiles) * BN;
+        const int v_lo = (int)(q0 / p.Wp) - p.PH;
+        const int nr = (int)((q0 + 127) / p.Wp) + p.PH - v_lo + 1;
+        // first image row: floor division (v_lo is -PH for the very first tile)
+        const int img = v_lo >= 0 ? v_lo / p.Hv : -1;
+        const int hrow = v_lo - img * p.Hv;
+        for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+          if (!mbar_wait(smem_u32(&bar_aempty[as]), aphase ^ 1u, abort_ptr, 11)) { ok = false; break; }
+          const uint32_t afull = smem_u32(&bar_afull[as]);
+          mbar_expect_tx(afull, (uint32_t)nr * row_bytes);
+          uint32_t dst = smem_base + as * p.a_stage_bytes + kRowLead;
+          int im = img, hr = hrow;
+          for (int r = 0; r < nr; ++r, dst += row_bytes) {
+            // rows h >= H (separators) and images outside [0, N) are filled with zeros by the copy
+            tma_load_4d(dst, &mapA, afull, cc * 32, -p.PW, hr, im);
+            if (++hr == p.Hv) { hr = 0; ++im; }
+          }
+          if (++as == kRowAStages) { as = 0; aphase ^= 1u; }
+          for (int tap0 = 0; tap0 < taps && !p.resident; tap0 += p.tps) {
+            const int cnt = taps - tap0 < p.tps ? taps - tap0 : p.tps;
+            if (!mbar_wait(smem_u32(&bar_bempty[bs]), bphase ^ 1u, abort_ptr, 12)) { ok = false; break; }
+            const uint32_t bfull = smem_u32(&bar_bfull[bs]);
+            mbar_expect_tx(bfull, (uint32_t)cnt * kTapBytes);
+            uint32_t b_dst = b_base + bs * b_stage_bytes;
+            for (int tap = tap0; tap < tap0 + cnt; ++tap, b_dst += kTapBytes) {
+              if (BMODE == B_KMAJOR) {
+                tma_load_2d(b_dst, &mapB, bfull, tap * p.kc_total + cc * 32, n0);
+              } else {
+#pragma unroll
+                for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, bfull, p.b_tap_x[tap] + n0 + 32 * j, cc * 32);
+              }
+            }
+            if (++bs == BST) { bs = 0; bphase ^= 1u; }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    // The whole warp runs the loops converged and one elected lane issues: with warp-uniform
+    // control flow the descriptors stay in uniform registers, which roughly halves the cost of
+    // issuing a tcgen05.mma compared with a lane-0 branch around everything.
+    constexpr uint32_t idesc = idesc_tf32(128, BN, 0, BMODE == B_MNMAJOR ? 1 : 0);
+    constexpr uint32_t a_hi = desc_hi_kmajor();
+    constexpr uint32_t b_hi = BMODE == B_MNMAJOR ? desc_hi_mnmajor() : desc_hi_kmajor();
+    constexpr uint32_t b_step = BMODE == B_MNMAJOR ? (1024u >> 4) : (32u >> 4);
+    constexpr uint32_t tap_step = kTapBytes >> 4;
+    const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(b_base) : desc_lo_kmajor(b_base);
+    const uint32_t row_step = (uint32_t)p.Wp * 8u;  // one image row, in 16-byte units (a pixel is 128 B)
+    int as = 0, bs = 0;
+    uint32_t aphase = 0, bphase = 0;
+    int t = 0;
+    bool ok = true;
+    if (p.resident && blockIdx.x < tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bres), 0, abort_ptr, 17));
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+      const long long q0 = (long long)(tile / p.n_tiles) * 128;
+      const int col = (int)(q0 % p.Wp);
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 13));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      for (int cc = 0; cc < p.cchunks && ok; ++cc) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_afull[as]), aphase, abort_ptr, 14));
+        if (!ok) break;
+        tc_fence_after();
+        // position q0 of this tile sits PH rows and `col` pixels into the staged rows; tap
+        // (kh, kw) reads (kh - PH) rows and (kw - PW) pixels away from it
+        const uint32_t a_tile = desc_lo_kmajor(smem_base + as * p.a_stage_bytes + kRowLead) + (uint32_t)((col - p.PW) * 8);
+        if (p.resident) {
+          const uint32_t b_cc = b_lo0 + (uint32_t)(cc * taps) * tap_step;
+          if (elect_one()) {
+            if (FK == 3) {
+#pragma unroll
+              for (int kh = 0; kh < 3; ++kh)
+#pragma unroll
+                for (int kw = 0; kw < 3; ++kw)
+#pragma unroll
+                  for (int k = 0; k < 4; ++k)
+                    mma_tf32_words(d_tmem, a_tile + kh * row_step + kw * 8 + 2 * k, a_hi, b_cc + (kh * 3 + kw) * tap_step + k * b_step, b_hi, idesc,
+                                   (kh + kw + k) ? 1u : (uint32_t)(cc > 0));
+            } else {
+              uint32_t a_row = a_tile, a_lo = a_tile, b_lo = b_cc;
+              int kw = 0;
+              for (int tap = 0; tap < taps; ++tap, b_lo += tap_step) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_tf32_words(d_tmem, a_lo + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc, (tap + k) ? 1u : (uint32_t)(cc > 0));
+                a_lo += 8u;
+                if (++kw == p.KW) { kw = 0; a_row += row_step; a_lo = a_row; }
+              }
+            }
+            mma_commit(smem_u32(&bar_aempty[as]));
+          }
+          __syncwarp();
+        } else {
+          int kh = 0, kw = 0;
+          for (int tap0 = 0; tap0 < taps && ok; tap0 += p.tps) {
+            const int cnt = taps - tap0 < p.tps ? taps - tap0 : p.tps;
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), bphase, abort_ptr, 15));
+            if (!ok) break;
+            tc_fence_after();
+            if (elect_one()) {
+              uint32_t b_lo = b_lo0 + bs * (b_stage_bytes >> 4);
+              uint32_t a_lo = a_tile + kh * row_step + kw * 8;
+              int w = kw;
+              for (int j = 0; j < cnt; ++j, b_lo += tap_step) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mma_tf32_words(d_tmem, a_lo + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc, (tap0 + j + k) ? 1u : (uint32_t)(cc > 0));
+                a_lo += 8u;
+                if (++w == p.KW) { w = 0; a_lo += row_step - (uint32_t)p.KW * 8u; }
+              }
+              mma_commit(smem_u32(&bar_bempty[bs]));
+            }
+            __syncwarp();
+            kw += cnt;
+            while (kw >= p.KW) { kw -= p.KW; ++kh; }
+            if (++bs == BST) { bs = 0; bphase ^= 1u; }
+          }
+          if (ok && elect_one()) mma_commit(smem_u32(&bar_aempty[as]));
+          __syncwarp();
+        }
+        if (++as == kRowAStages) { as = 0; aphase ^= 1u; }
+      }
+      if (ok && elect_one()) mma_commit(smem_u32(&bar_tfull[buf]));
+      __syncwarp();
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    int t = 0;
+    const bool vec_ok = (p.ldo % 4 == 0) && (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias)) & 15u) == 0);
+    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
+      const long long q = (long long)(tile / p.n_tiles) * 128 + quarter * 32 + lane;
+      const int n0 = (tile % p.n_tiles) * BN;
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      // position -> pixel; padding columns and separator rows have no output
+      const long long v = q / p.Wp;
+      const int wp = (int)(q - v * p.Wp);
+      const long long img = v / p.Hv;
+      const int hrow = (int)(v - img * p.Hv);
+      const bool valid = q < p.Q && hrow < p.H && wp >= p.PW && wp < p.W + p.PW;
+      float* orow = p.out + ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
+      bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 16);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+        tmem_ld_wait();
+        const int col0 = n0 + c0;
+        if (valid && col0 < p.N) {
+          if (vec_ok && col0 + 32 <= p.N) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4) {
+              float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+              if (p.bias) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+              }
+              if (p.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+              *reinterpret_cast<float4*>(orow + col0 + j) = o;
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              if (col0 + j < p.N) {
+                float o = __uint_as_float(r[j]);
+                if (p.bias) o += p.bias[col0 + j];
+                if (p.relu) o = fmaxf(o, 0.f);
+                orow[col0 + j] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+    }
+  }
+
+  // ------------------------------------------------------------ teardown
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);  // let copies in flight land before shared memory is released
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 2 * BN);
+  }
+}
+
+// Geometry and shared-memory plan; `ok` is false when the shape is outside what the kernel
+// handles or when too much of the work would land on padding.
+struct RowConvPlan {
+  bool ok;
+  int Wp, Hv, nr_max, b_stages, tps, resident;
+  uint32_t a_stage_bytes, smem_bytes;
+};
+
+RowConvPlan row_conv_plan(int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int kc, int nout, int bn) {
+  RowConvPlan r{};
+  if (getenv("MTB_DISABLE_ROWCONV")) return r;
+  if (sh != 1 || sw != 1 || kh != 2 * ph + 1 || kw != 2 * pw + 1 || kh * kw < 2 || kh * kw > 64 || pw > 7 || kc % 32) return r;
+  r.Wp = w + 2 * pw;
+  r.Hv = h + ph;
+  if (r.Wp > 256) return r;
+  if ((double)w * h < 0.8 * (double)r.Wp * r.Hv) return r;  // too much padding: the im2col kernel wastes nothing
+  r.nr_max = (r.Wp - 1 + 127) / r.Wp + 1 + 2 * ph;
+  const uint32_t need = kRowLead + (uint32_t)(r.nr_max * r.Wp + pw + 8) * 128u;
+  r.a_stage_bytes = (need + 1023u) & ~1023u;
+  const uint32_t budget = 227u * 1024u - 2048u;
+  const uint32_t fixed = 1024u + kRowAStages * r.a_stage_bytes;
+  const uint32_t tap_bytes = (uint32_t)bn * 128u;
+  if (fixed + 3u * tap_bytes > budget) return r;
+  const int taps = kh * kw;
+  const uint32_t filter_bytes = (uint32_t)taps * (kc / 32) * tap_bytes;
+  if (nout <= bn && fixed + filter_bytes <= budget) {  // the whole filter fits beside the activation ring
+    r.resident = 1;
+    r.tps = taps;
+    r.b_stages = 1;
+    r.smem_bytes = fixed + filter_bytes;
+    r.ok = true;
+    return r;
+  }
+  // the most taps per weight stage that still leaves two stages (hand-overs are expensive)
+  int tps = (int)((budget - fixed) / (2u * tap_bytes));
+  if (tps > taps) tps = taps;
+  if (bn >= 256 || tps < 2) tps = 1;  // N = 256: four MMAs already outlast a hand-over
+  r.tps = tps;
+  int bst = (int)((budget - fixed) / (tps * tap_bytes));
+  r.b_stages = bst > 8 ? 8 : bst;
+  r.smem_bytes = fixed + r.b_stages * tps * tap_bytes;
+  r.ok = true;
+  return r;
+}
+
+template <int BN, int BMODE, int FK>
+int launch_row_conv(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
+  auto kernel = tc_conv_rows_kernel<BN, BMODE, FK>;
+  static bool configured = false;
+  if (!configured) {
+    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+    configured = true;
+  }
+  const int tiles = p.m_tiles * p.n_tiles;
+  const int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
+  kernel<<<grid, 192, smem_bytes, st>>>(mapA, mapB, p);
+  MTB_LAUNCH_CHECK("tc_conv_rows_kernel");
+  return MTB_OK;
+}
+
+template <int BMODE>
+int launch_row_conv_bn(int bn, const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
+  const bool k3 = p.KH == 3 && p.KW == 3;  // the 3x3 filter has its MMA sequence unrolled
+  if (bn == 64) return k3 ? launch_row_conv<64, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<64, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
+  if (bn == 128) return k3 ? launch_row_conv<128, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<128, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
+  return k3 ? launch_row_conv<256, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<256, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
+}
+
+// Shared by forward (x, K-major weights) and the stride-1 data gradient (dY, weights in place).
+// act: [N, H, W, kc] channels-last; out: [N, H, W, nout].
+template <int BMODE>
+int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, int kh, int kw, int ph, int pw, int nout, const float* act,
+                 const CUtensorMap& mapB, const int* b_tap_x, const float* bias, int relu, float* out, cudaStream_t st) {
+  CUtensorMap mapA;
+  int rc = tc::encode_rows_4d(&mapA, act, n, h, w, kc, 32, plan.Wp);
+  if (rc) return rc;
+  RowConvParams p{};
+  p.Q = (long long)n * plan.Hv * plan.Wp;
+  p.Wp = plan.Wp; p.Hv = plan.Hv; p.H = h; p.W = w; p.PH = ph; p.PW = pw; p.KH = kh; p.KW = kw;
+  p.cchunks = kc / 32; p.kc_total = kc; p.N = nout;
+  p.m_tiles = (int)((p.Q + 127) / 128); p.n_tiles = (nout + bn - 1) / bn;
+  p.a_stage_bytes = plan.a_stage_bytes; p.b_stages = plan.b_stages; p.tps = plan.tps; p.resident = plan.resident;
+  p.out = out; p.ldo = nout; p.bias = bias; p.relu = relu;
+  if (b_tap_x) for (int j = 0; j < kh * kw; ++j) p.b_tap_x[j] = b_tap_x[j];
+  return launch_row_conv_bn<BMODE>(bn, mapA, mapB, p, plan.smem_bytes, st);
+}
+
+}  // namespace

@@ -60,6 +60,19 @@ int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long lo
   return MTB_OK;
 }
 
+int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w) {
+  int rc = load_driver_entry_points();
+  if (rc) return rc;
+  cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
+  cuuint64_t strides[3] = {(cuuint64_t)c * 4, (cuuint64_t)w * c * 4, (cuuint64_t)h * w * c * 4};
+  cuuint32_t box[4] = {(cuuint32_t)channels, (cuuint32_t)box_w, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = g_encode_tiled(map, tma_dtype(), 4, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeTiled (rows) failed (%d) n=%d h=%d w=%d c=%d box_w=%d", (int)r, n, h, w, c, box_w);
+  return MTB_OK;
+}
+
 int encode_im2col_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int lower_w, int lower_h, int upper_w, int upper_h,
                      int stride_w, int stride_h, int channels, int pixels, bool mn_major) {
   int rc = load_driver_entry_points();
@@ -136,7 +149,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
-      mbar_init(smem_u32(&bar_tempty[b]), 128);
+      mbar_init(smem_u32(&bar_tempty[b]), 4);  // one arrival per epilogue warp
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -247,7 +260,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
-      bool ok = mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 4);
+      // one lane polls (128 threads spinning on the barrier slow the other roles' barrier traffic down)
+      bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 4);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -291,7 +305,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&bar_tempty[buf]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
   }
 
@@ -351,6 +366,8 @@ bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 constexpr long long kMinIm2colBytes = 128 * 1024;
 
 }  // namespace
+
+#include "tc_conv_rows.cuh"
 
 // ------------------------------------------------------------------------------ host API
 
@@ -417,9 +434,11 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
   const long long M = (long long)n * oh * ow, K = (long long)kh * kw * cin;
   const int bn = pick_bn_for(cout, M);
   CUtensorMap mapA, mapB;
-  int rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
+  int rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
   if (rc) return rc;
-  rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
+  const RowConvPlan plan = row_conv_plan(h, w, kh, kw, sh, sw, ph, pw, cin, cout, bn);
+  if (plan.ok) return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, relu, y, (cudaStream_t)stream);
+  rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
   if (rc) return rc;
   GemmParams p{};
   p.M = (int)M; p.N = cout; p.num_kb = (int)(K / 32);
@@ -457,6 +476,14 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   CUtensorMap mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32, true);
   if (rc) return rc;
+  const RowConvPlan plan = row_conv_plan(h, w, kh, kw, sh, sw, ph, pw, cout, cin, bn);
+  if (plan.ok) {
+    // stride 1: dX = dY convolved with the filter rotated by 180 degrees, same padding
+    int tap_x[64];
+    for (int jh = 0; jh < kh; ++jh)
+      for (int jw = 0; jw < kw; ++jw) tap_x[jh * kw + jw] = ((kh - 1 - jh) * kw + (kw - 1 - jw)) * cin;
+    return run_row_conv<B_MNMAJOR>(plan, bn, n, h, w, cout, kh, kw, ph, pw, cin, dy, mapB, tap_x, nullptr, 0, dx, st);
+  }
   struct Axis { int taps, start, count, lower, upper; };
   auto axis = [](int a, int size, int osize, int k, int s, int pad) {
     Axis r{};
@@ -558,7 +585,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(smem_u32(&bar_tfull[b]), 1);
-      mbar_init(smem_u32(&bar_tempty[b]), 128);
+      mbar_init(smem_u32(&bar_tempty[b]), 4);  // one arrival per epilogue warp
     }
     abort_flag = 0;
     fence_barrier_init();
@@ -666,7 +693,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       const bool empty_unit = kb0 >= p.kb_total;  // cannot happen with the host's split choice; kept for safety
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
-      bool ok = mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 14);
+      // one lane polls (128 threads spinning on the barrier slow the other roles' barrier traffic down)
+      bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 14);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
@@ -694,7 +722,8 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
         }
       }
       tc_fence_before();
-      mbar_arrive(smem_u32(&bar_tempty[buf]));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
   }
 

@@ -54,7 +54,7 @@ class GradBucket:
             self.flat = torch.zeros(self.total, dtype=torch.float32, device=where)
         return self.flat
 
-    def pack(self, scale):
+    def pack(self, scale, stream=None):
         """flat[offset_k : offset_k + n_k] = scale * grad_k for every parameter."""
         flat = self._ensure_flat()
         if self.params[0].device.type == "cpu":
@@ -69,7 +69,7 @@ class GradBucket:
         srcs = (ctypes.c_void_p * k)(*[p.grad._native_array.ptr for p in self.params])
         offs = (ctypes.c_longlong * k)(*self.offsets)
         sizes = (ctypes.c_longlong * k)(*self.sizes)
-        env.lib.pack_scale_f32(k, srcs, offs, sizes, flat.data_ptr(), float(scale), env.stream())
+        env.lib.pack_scale_f32(k, srcs, offs, sizes, flat.data_ptr(), float(scale), env.stream() if stream is None else stream)
         return flat
 
     def point_grads_at_flat(self):
@@ -89,17 +89,61 @@ class GradBucket:
             p.grad = g
 
 
-class DataParallel:
-    """Wraps a module; ``reduce_gradients()`` goes between ``loss.backward()`` and ``optimizer.step()``."""
+def split_into_buckets(params, count):
+    """Split parameters, taken in reverse order of use (the order in which backward finishes
+    them), into `count` contiguous groups of roughly equal size in bytes."""
+    rev = list(params)[::-1]
+    sizes = [int(np.prod(p.shape, dtype=np.int64)) for p in rev]
+    total, groups, cur, acc = sum(sizes), [], [], 0
+    for p, n in zip(rev, sizes):
+        cur.append(p)
+        acc += n
+        if len(groups) < count - 1 and acc >= total * (len(groups) + 1) / count:
+            groups.append(cur)
+            cur = []
+    if cur:
+        groups.append(cur)
+    return groups
 
-    def __init__(self, module, process_group=None):
+
+class DataParallel:
+    """Wraps a module; ``reduce_gradients()`` goes between ``loss.backward()`` and ``optimizer.step()``.
+
+    With ``buckets > 1`` the all-reduce of a bucket starts as soon as backward has produced the
+    last gradient of that bucket (the deepest layers finish first); on CUDA it runs on a side
+    stream, so it overlaps the rest of backward and ``reduce_gradients()`` only waits for it.
+    """
+
+    def __init__(self, module, process_group=None, buckets=2):
         import torch.distributed as dist
 
         self.module = module
         self.group = process_group
         self.world = dist.get_world_size(process_group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
-        self.bucket = GradBucket(module.parameters()) if self.world > 1 else None
+        self.buckets, self._bucket_of, self._remaining, self._events = [], {}, [], []
+        self._side = None
+        if self.world > 1:
+            params = list(module.parameters())
+            on_cuda = params[0].device.type == "cuda"
+            groups = split_into_buckets(params, buckets)
+            self.buckets = [GradBucket(g) for g in groups]
+            for b, g in enumerate(groups):
+                for p in g:
+                    self._bucket_of[id(p)] = b
+            if len(self.buckets) > 1:
+                from mytorch_b200.autograd import DAGTracker
+
+                if on_cuda:
+                    import torch
+
+                    self._side = torch.cuda.Stream()
+                DAGTracker.instance().leaf_grad_final_hook = self._on_grad_final
+            self._reset()
+
+    def _reset(self):
+        self._remaining = [len(b.params) for b in self.buckets]
+        self._events = [None] * len(self.buckets)
 
     def __call__(self, *args, **kwargs):
         return self.module(*args, **kwargs)
@@ -110,14 +154,48 @@ class DataParallel:
     def shard(self, array):
         return shard_batch(array, self.rank, self.world)
 
+    def _launch_bucket(self, b, stream=None):
+        import torch
+        import torch.distributed as dist
+
+        bucket = self.buckets[b]
+        if stream is None:
+            flat = bucket.pack(1.0 / self.world)
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            return
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream())
+        with torch.cuda.stream(stream):
+            stream.wait_event(ready)
+            flat = bucket.pack(1.0 / self.world, stream=stream.cuda_stream)
+            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            done = torch.cuda.Event()
+            done.record(stream)
+        self._events[b] = done
+
+    def _on_grad_final(self, tensor):
+        b = self._bucket_of.get(id(tensor))
+        if b is None:
+            return
+        self._remaining[b] -= 1
+        if self._remaining[b] == 0:
+            self._launch_bucket(b, self._side)
+
     def reduce_gradients(self):
         if self.world == 1:
             return
-        import torch.distributed as dist
+        import torch
 
-        flat = self.bucket.pack(1.0 / self.world)
-        dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
-        self.bucket.point_grads_at_flat()
+        for b, bucket in enumerate(self.buckets):
+            if self._remaining[b] > 0:  # not started by the hook (gradients were set by hand, or no hook)
+                self._launch_bucket(b, self._side)
+        if self._side is not None:
+            for ev in self._events:
+                if ev is not None:
+                    torch.cuda.current_stream().wait_event(ev)
+        for bucket in self.buckets:
+            bucket.point_grads_at_flat()
+        self._reset()
 
     def broadcast_parameters(self, src=0):
         """Make every replica start from rank ``src``'s parameters and buffers."""
