@@ -77,6 +77,10 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap* map
                ::"r"(dst), "l"(map), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n)
                : "memory");
 }
+// the same box, only brought into L2 (no shared-memory destination, no completion to wait for)
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap* map, int c, int w, int h, int n) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c), "r"(w), "r"(h), "r"(n) : "memory");
+}
 // im2col mode over a channels-last tensor {C, W, H, N}: c/w/h/n locate the first pixel (in
 // input coordinates, i.e. already multiplied by the stride and shifted by -padding); off_w/off_h
 // are the filter-tap offsets.
@@ -208,7 +212,7 @@ int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long lo
                     bool mn_major = false);
 // channels-last activation {C, W, H, N}; a load takes `box_w` consecutive pixels of one image
 // row x `channels` channels (tiled mode, 128-byte swizzle, zero fill outside the tensor).
-int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w);
+int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w, bool mn_major = false);
 // channels-last activation {C, W, H, N}; a load takes `pixels` output pixels x `channels`
 // channels for one filter tap of a convolution with the given stride / lower padding; `upper`
 // = lower_pad - (filter - 1) per spatial dim bounds the walk of the window origin.

@@ -411,3 +411,335 @@ int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, i
 }
 
 }  // namespace
+
+// ------------------------------------------------------------------------------ weight gradient
+//
+// dW[co][kh][kw][ci] = sum over positions q of dY[q][co] * X[q + (kh-PH)*Wp + (kw-PW)][ci], in the
+// same padded linear position space as above (dY is staged with the same zero-filled padding
+// columns and separator rows, so padding positions contribute nothing).  Both operands lie in
+// shared memory as [position][32 channels] panels, which tcgen05 reads as MN-major operands with
+// the position as the reduction index.  A filter tap is a shift of the X panel by whole rows, and
+// the four 32-wide M blocks of one MMA are the SAME X panel shifted by 0, 1, 2, 3 positions
+// (descriptor LBO = 128 bytes): one MMA covers kw = 0..3 of one filter row for 32 input channels
+// (for a 3-wide filter the fourth block is computed and dropped).  X and dY are therefore staged
+// once per block of 128 positions instead of once per tap, which is what bounded the im2col
+// form (the copy engine pays per 128-byte pixel row it gathers).
+//
+// One CTA = one unit (group of input-channel blocks, range of position blocks); it keeps one
+// accumulator of BN columns per (channel block, filter row, group of 4 taps) in tensor memory and
+// writes them as an fp32 partial; the partials are added in a fixed order afterwards.
+namespace {
+
+struct WgradRowsParams {
+  long long Q;
+  int Wp, Hv, H, W, PH, PW, KH, KW;
+  int Cin, Cout;
+  int ncc_g;     // channel blocks of 32 per group
+  int n_kwg;     // ceil(KW / 4)
+  int splits, kb_total, kb_per_split;  // position blocks of 128
+  uint32_t x_panel_bytes, y_panel_bytes, stage_bytes;
+  float* partial;  // [splits][KH*KW*Cin][Cout]
+};
+
+constexpr int kWgRowsStages = 2;
+constexpr int kWgRowsPB = 128;  // positions per stage
+
+// FIX > 0: 3-tall, at most 4-wide filter with exactly FIX channel blocks per CTA; the MMA sequence of
+// a stage is then straight-line code (issuing from runtime loops costs twice the cycles per MMA).
+template <int BN, int FIX>
+__global__ void __launch_bounds__(192, 1)
+tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant__ CUtensorMap mapDY, const WgradRowsParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_full[kWgRowsStages], bar_empty[kWgRowsStages], bar_tfull;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+
+  // lead / tail rows of the panels are read (against zero gradients only) but never written
+  for (uint32_t i = threadIdx.x; i < kWgRowsStages * p.stage_bytes / 16; i += blockDim.x)
+    reinterpret_cast<uint4*>(smem_raw + (smem_base - smem_u32(smem_raw)))[i] = make_uint4(0, 0, 0, 0);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kWgRowsStages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&bar_tfull), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 512);
+    tmem_relinquish();
+  }
+  fence_proxy_async();
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = tmem_slot;
+  volatile int* abort_ptr = &abort_flag;
+
+  const int group = blockIdx.x / p.splits, split = blockIdx.x - group * p.splits;
+  const int cchunks = p.Cin / 32;
+  const int cc0 = group * p.ncc_g;
+  const int ncc = cchunks - cc0 < p.ncc_g ? cchunks - cc0 : p.ncc_g;
+  const int kb0 = split * p.kb_per_split;
+  const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
+  const uint32_t row_bytes = (uint32_t)p.Wp * 128u;
+  const uint32_t y_off = (uint32_t)p.ncc_g * p.x_panel_bytes;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      prefetch_tensormap(&mapX);
+      prefetch_tensormap(&mapDY);
+      int stage = 0;
+      uint32_t phase = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        const long long q0 = (long long)kb * kWgRowsPB;
+        const int v0 = (int)(q0 / p.Wp);
+        const int nr_y = (int)((q0 + kWgRowsPB - 1) / p.Wp) - v0 + 1;
+        const int nr_x = nr_y + 2 * p.PH;
+        if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 21)) break;
+        const uint32_t full = smem_u32(&bar_full[stage]);
+        mbar_expect_tx(full, (uint32_t)(nr_x * ncc + nr_y * (BN / 32)) * row_bytes);
+        const uint32_t st = smem_base + stage * p.stage_bytes;
+        {
+          const int v = v0 - p.PH;
+          int im = v >= 0 ? v / p.Hv : -1, hr = v - im * p.Hv;
+          uint32_t dst = st + kRowLead;
+          for (int r = 0; r < nr_x; ++r, dst += row_bytes) {
+            for (int c = 0; c < ncc; ++c) tma_load_4d(dst + c * p.x_panel_bytes, &mapX, full, (cc0 + c) * 32, -p.PW, hr, im);
+            if (++hr == p.Hv) { hr = 0; ++im; }
+          }
+        }
+        {
+          int im = v0 / p.Hv, hr = v0 - im * p.Hv;
+          uint32_t dst = st + y_off;
+          for (int r = 0; r < nr_y; ++r, dst += row_bytes) {
+#pragma unroll
+            for (int j = 0; j < BN / 32; ++j) tma_load_4d(dst + j * p.y_panel_bytes, &mapDY, full, j * 32, -p.PW, hr, im);
+            if (++hr == p.Hv) { hr = 0; ++im; }
+          }
+        }
+        if (++stage == kWgRowsStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (converged warp, elected issue)
+    constexpr uint32_t idesc = idesc_tf32(128, BN, 1, 1);
+    constexpr uint32_t hi = desc_hi_mnmajor();
+    const uint32_t wp8 = (uint32_t)p.Wp * 8u;  // one image row in 16-byte units
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    int col0 = (int)(((long long)kb0 * kWgRowsPB) % p.Wp);
+    for (int kb = kb0; kb < kb1 && ok; ++kb) {
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 22));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_base + stage * p.stage_bytes;
+      // position q0 sits PH rows and col0 pixels into the X rows, col0 pixels into the dY rows
+      const uint32_t x_lo = desc_lo_mnmajor(st + kRowLead, 128u) + (uint32_t)((col0 - p.PW) * 8);
+      const uint32_t y_lo = desc_lo_mnmajor(st + y_off, p.y_panel_bytes) + (uint32_t)(col0 * 8);
+      const uint32_t x_panel = p.x_panel_bytes >> 4;
+      if (elect_one()) {
+        if (FIX > 0) {
+          const uint32_t first = kb > kb0 ? 1u : 0u;
+#pragma unroll
+          for (int ks = 0; ks < kWgRowsPB / 8; ++ks)  // 8 positions per MMA; 8 rows of 128 B = 64 units
+#pragma unroll
+            for (int c = 0; c < FIX; ++c)
+#pragma unroll
+              for (int kh = 0; kh < 3; ++kh)
+                mma_tf32_words(tmem_base + (c * 3 + kh) * BN, x_lo + c * x_panel + kh * wp8 + ks * 64u, hi, y_lo + ks * 64u, hi, idesc, ks ? 1u : first);
+        } else {
+          for (int ks = 0; ks < kWgRowsPB / 8; ++ks) {
+            const uint32_t accum = (kb > kb0 || ks > 0) ? 1u : 0u;
+            const uint32_t yk = y_lo + ks * 64u;
+            uint32_t d = tmem_base;
+            for (int c = 0; c < ncc; ++c) {
+              uint32_t xk = x_lo + c * x_panel + ks * 64u;
+              for (int kh = 0; kh < p.KH; ++kh, xk += wp8)
+                for (int g = 0; g < p.n_kwg; ++g, d += BN) mma_tf32_words(d, xk + g * 32u, hi, yk, hi, idesc, accum);
+            }
+          }
+        }
+        mma_commit(smem_u32(&bar_empty[stage]));
+      }
+      __syncwarp();
+      col0 = (col0 + kWgRowsPB) % p.Wp;
+      if (++stage == kWgRowsStages) { stage = 0; phase ^= 1u; }
+    }
+    if (ok && elect_one()) mma_commit(smem_u32(&bar_tfull));
+    __syncwarp();
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int quarter = warp & 3;
+    bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull), 0, abort_ptr, 23);
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      tc_fence_after();
+      const long long Kw = (long long)p.KH * p.KW * p.Cin;
+      float* part = p.partial + (long long)split * Kw * p.Cout;
+      const bool vec_ok = (p.Cout % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.partial) & 15u) == 0);
+      int a = 0;
+      for (int c = 0; c < ncc; ++c)
+        for (int kh = 0; kh < p.KH; ++kh)
+          for (int g = 0; g < p.n_kwg; ++g, ++a) {
+            const int kw = g * 4 + quarter;             // M block = tap within the group of four
+            const int ci = (cc0 + c) * 32 + lane;
+            const bool valid = kw < p.KW && ci < p.Cin;
+            float* orow = part + ((long long)(kh * p.KW + kw) * p.Cin + ci) * p.Cout;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+              uint32_t r[32];
+              tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN + c0), r);
+              tmem_ld_wait();
+              if (valid && c0 < p.Cout) {
+                if (vec_ok && c0 + 32 <= p.Cout) {
+#pragma unroll
+                  for (int j = 0; j < 32; j += 4)
+                    *reinterpret_cast<float4*>(orow + c0 + j) =
+                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                } else {
+#pragma unroll
+                  for (int j = 0; j < 32; ++j)
+                    if (c0 + j < p.Cout) orow[c0 + j] = __uint_as_float(r[j]);
+                }
+              }
+            }
+          }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (abort_flag) {
+    for (int i = 0; i < 64; ++i) __nanosleep(2000);
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+// dw[co][r] = sum_s partial[s][r][co] with the splits spread over 8 thread groups (group z adds
+// splits z, z+8, ... in order; the 8 sums are then added in index order): the same result for
+// any launch, and enough CTAs to read ~100 partial planes at full speed.
+__global__ void __launch_bounds__(1024) wgrad_reduce_many_kernel(const float* __restrict__ partial, float* __restrict__ dw, int Kw, int Cout, int splits) {
+  __shared__ float acc[8][4][33];
+  const int c = blockIdx.y * 32 + threadIdx.x;
+  const int r = blockIdx.x * 4 + threadIdx.y;
+  const int z0 = threadIdx.z;
+  const long long plane = (long long)Kw * Cout;
+  float s0 = 0.f, s1 = 0.f;
+  if (r < Kw && c < Cout) {
+    const float* q = partial + (long long)r * Cout + c;
+    int z = z0;
+    for (; z + 8 < splits; z += 16) { s0 += q[z * plane]; s1 += q[(z + 8) * plane]; }
+    if (z < splits) s0 += q[z * plane];
+  }
+  acc[z0][threadIdx.y][threadIdx.x] = s0 + s1;
+  __syncthreads();
+  if (z0 == 0 && r < Kw && c < Cout) {
+    float t = acc[0][threadIdx.y][threadIdx.x];
+#pragma unroll
+    for (int k = 1; k < 8; ++k) t += acc[k][threadIdx.y][threadIdx.x];
+    dw[(long long)c * Kw + r] = t;
+  }
+}
+
+struct WgradRowsPlan {
+  bool ok;
+  int bn, Wp, Hv, ncc_g, groups, n_kwg, splits, kb_total, kb_per_split;
+  uint32_t x_panel_bytes, y_panel_bytes, stage_bytes, smem_bytes;
+};
+
+WgradRowsPlan wgrad_rows_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
+  WgradRowsPlan r{};
+  if (getenv("MTB_DISABLE_ROWCONV") || getenv("MTB_DISABLE_ROWWGRAD")) return r;
+  if (sh != 1 || sw != 1 || kh != 2 * ph + 1 || kw != 2 * pw + 1 || kh * kw < 2 || pw > 7 || cin % 32 || cout > 128 || cout % 4) return r;
+  r.bn = cout <= 64 ? 64 : 128;
+  r.Wp = w + 2 * pw;
+  r.Hv = h + ph;
+  r.n_kwg = (kw + 3) / 4;
+  if (r.Wp > 256) return r;
+  // useful share of the MMA work: padding positions and the unused taps of the last group of four
+  if ((double)w * h * kw < 0.6 * (double)r.Wp * r.Hv * (4 * r.n_kwg)) return r;
+  const int nr_y = (r.Wp - 1 + kWgRowsPB - 1) / r.Wp + 1, nr_x = nr_y + 2 * ph;
+  r.x_panel_bytes = (kRowLead + (uint32_t)(nr_x * r.Wp + 16) * 128u + 1023u) & ~1023u;
+  r.y_panel_bytes = ((uint32_t)(nr_y * r.Wp) * 128u + 1023u) & ~1023u;
+  const uint32_t budget = 227u * 1024u - 3072u;
+  const int cchunks = cin / 32;
+  int best = 0;
+  for (int g = 1; g <= cchunks; ++g) {
+    if (kh * r.n_kwg * g * r.bn > 512) break;
+    const uint32_t stage = g * r.x_panel_bytes + (r.bn / 32) * r.y_panel_bytes;
+    if (kWgRowsStages * stage > budget) break;
+    best = g;
+  }
+  if (best == 0) return r;
+  r.ncc_g = best;
+  r.groups = (cchunks + best - 1) / best;
+  r.stage_bytes = best * r.x_panel_bytes + (r.bn / 32) * r.y_panel_bytes;
+  r.smem_bytes = kWgRowsStages * r.stage_bytes + 1024;
+  const long long Q = (long long)n * r.Hv * r.Wp;
+  r.kb_total = (int)((Q + kWgRowsPB - 1) / kWgRowsPB);
+  int splits = mtb_sm_count() / r.groups;
+  if (splits < 1) splits = 1;
+  if (splits > r.kb_total) splits = r.kb_total;
+  r.kb_per_split = (r.kb_total + splits - 1) / splits;
+  r.splits = (r.kb_total + r.kb_per_split - 1) / r.kb_per_split;
+  r.ok = true;
+  return r;
+}
+
+template <int BN, int FIX>
+int launch_wgrad_rows(const CUtensorMap& mapX, const CUtensorMap& mapDY, const WgradRowsParams& p, int grid, uint32_t smem_bytes, cudaStream_t st) {
+  auto kernel = tc_wgrad_rows_kernel<BN, FIX>;
+  static bool configured = false;
+  if (!configured) {
+    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
+    configured = true;
+  }
+  kernel<<<grid, 192, smem_bytes, st>>>(mapX, mapDY, p);
+  MTB_LAUNCH_CHECK("tc_wgrad_rows_kernel");
+  return MTB_OK;
+}
+
+int run_wgrad_rows(const WgradRowsPlan& q, int n, int cin, int h, int w, int kh, int kw, int ph, int pw, int cout, const float* x, const float* dy,
+                   float* dw, float* partial, cudaStream_t st) {
+  CUtensorMap mapX, mapDY;
+  int rc = tc::encode_rows_4d(&mapX, x, n, h, w, cin, 32, q.Wp, true);
+  if (rc) return rc;
+  rc = tc::encode_rows_4d(&mapDY, dy, n, h, w, cout, 32, q.Wp, true);
+  if (rc) return rc;
+  WgradRowsParams p{};
+  p.Q = (long long)n * q.Hv * q.Wp;
+  p.Wp = q.Wp; p.Hv = q.Hv; p.H = h; p.W = w; p.PH = ph; p.PW = pw; p.KH = kh; p.KW = kw;
+  p.Cin = cin; p.Cout = cout; p.ncc_g = q.ncc_g; p.n_kwg = q.n_kwg;
+  p.splits = q.splits; p.kb_total = q.kb_total; p.kb_per_split = q.kb_per_split;
+  p.x_panel_bytes = q.x_panel_bytes; p.y_panel_bytes = q.y_panel_bytes; p.stage_bytes = q.stage_bytes;
+  p.partial = partial;
+  const int grid = q.groups * q.splits;
+  // straight-line MMA sequence when every CTA has the same, small number of channel blocks
+  const int fix = (kh == 3 && q.n_kwg == 1 && (cin / 32) % q.ncc_g == 0 && q.ncc_g <= 2) ? q.ncc_g : 0;
+  if (q.bn == 64) {
+    rc = fix == 2 ? launch_wgrad_rows<64, 2>(mapX, mapDY, p, grid, q.smem_bytes, st)
+       : fix == 1 ? launch_wgrad_rows<64, 1>(mapX, mapDY, p, grid, q.smem_bytes, st)
+                  : launch_wgrad_rows<64, 0>(mapX, mapDY, p, grid, q.smem_bytes, st);
+  } else {
+    rc = fix == 1 ? launch_wgrad_rows<128, 1>(mapX, mapDY, p, grid, q.smem_bytes, st) : launch_wgrad_rows<128, 0>(mapX, mapDY, p, grid, q.smem_bytes, st);
+  }
+  if (rc) return rc;
+  const int Kw = kh * kw * cin;
+  dim3 rgrid((unsigned)((Kw + 3) / 4), (unsigned)((cout + 31) / 32));
+  wgrad_reduce_many_kernel<<<rgrid, dim3(32, 4, 8), 0, st>>>(partial, dw, Kw, cout, q.splits);
+  MTB_LAUNCH_CHECK("wgrad_reduce_many_kernel");
+  return MTB_OK;
+}
+
+}  // namespace

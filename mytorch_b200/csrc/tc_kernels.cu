@@ -60,7 +60,7 @@ int encode_tiled_2d(CUtensorMap* map, const float* base, long long rows, long lo
   return MTB_OK;
 }
 
-int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w) {
+int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int c, int channels, int box_w, bool mn_major) {
   int rc = load_driver_entry_points();
   if (rc) return rc;
   cuuint64_t dims[4] = {(cuuint64_t)c, (cuuint64_t)w, (cuuint64_t)h, (cuuint64_t)n};
@@ -68,7 +68,8 @@ int encode_rows_4d(CUtensorMap* map, const float* base, int n, int h, int w, int
   cuuint32_t box[4] = {(cuuint32_t)channels, (cuuint32_t)box_w, 1, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = g_encode_tiled(map, tma_dtype(), 4, const_cast<float*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                              mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B : CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return mtb_fail(MTB_ERR_CUDA, "cuTensorMapEncodeTiled (rows) failed (%d) n=%d h=%d w=%d c=%d box_w=%d", (int)r, n, h, w, c, box_w);
   return MTB_OK;
 }
@@ -217,39 +218,46 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     }
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(128, BN, AMODE == A_MNMAJOR ? 1 : 0, BMODE == B_MNMAJOR ? 1 : 0);
-      constexpr uint32_t a_hi = AMODE == A_MNMAJOR ? desc_hi_mnmajor() : desc_hi_kmajor();
-      constexpr uint32_t b_hi = BMODE == B_MNMAJOR ? desc_hi_mnmajor() : desc_hi_kmajor();
-      constexpr uint32_t a_step = AMODE == A_MNMAJOR ? (1024u >> 4) : (32u >> 4);  // per 8 of K, in 16-byte units
-      constexpr uint32_t b_step = BMODE == B_MNMAJOR ? (1024u >> 4) : (32u >> 4);
-      const uint32_t a_lo0 = AMODE == A_MNMAJOR ? desc_lo_mnmajor(smem_base) : desc_lo_kmajor(smem_base);
-      const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(smem_base + C::kABytes) : desc_lo_kmajor(smem_base + C::kABytes);
-      int stage = 0;
-      uint32_t phase = 0;
-      int t = 0;
-      bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
-        const int buf = t & 1;
-        const uint32_t use = (uint32_t)(t >> 1);
-        if (!mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 2)) { ok = false; break; }
+    // The whole warp runs the loop converged and one elected lane issues (warp-uniform control
+    // flow keeps the descriptors in uniform registers: a lane-0 branch around the loop costs
+    // about twice as many cycles per tcgen05.mma).
+    constexpr uint32_t idesc = idesc_tf32(128, BN, AMODE == A_MNMAJOR ? 1 : 0, BMODE == B_MNMAJOR ? 1 : 0);
+    constexpr uint32_t a_hi = AMODE == A_MNMAJOR ? desc_hi_mnmajor() : desc_hi_kmajor();
+    constexpr uint32_t b_hi = BMODE == B_MNMAJOR ? desc_hi_mnmajor() : desc_hi_kmajor();
+    constexpr uint32_t a_step = AMODE == A_MNMAJOR ? (1024u >> 4) : (32u >> 4);  // per 8 of K, in 16-byte units
+    constexpr uint32_t b_step = BMODE == B_MNMAJOR ? (1024u >> 4) : (32u >> 4);
+    const uint32_t a_lo0 = AMODE == A_MNMAJOR ? desc_lo_mnmajor(smem_base) : desc_lo_kmajor(smem_base);
+    const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(smem_base + C::kABytes) : desc_lo_kmajor(smem_base + C::kABytes);
+    int stage = 0;
+    uint32_t phase = 0;
+    int t = 0;
+    bool ok = true;
+    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 2));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      uint32_t acc = 0;
+      for (int kb = 0; kb < p.num_kb; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 3));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        uint32_t acc = 0;
-        for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 3)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
+        const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
+        if (elect_one()) {
           mma_tf32_words(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, acc);
           mma_tf32_words(d_tmem, a_lo + a_step, a_hi, b_lo + b_step, b_hi, idesc, 1u);
           mma_tf32_words(d_tmem, a_lo + 2 * a_step, a_hi, b_lo + 2 * b_step, b_hi, idesc, 1u);
           mma_tf32_words(d_tmem, a_lo + 3 * a_step, a_hi, b_lo + 3 * b_step, b_hi, idesc, 1u);
-          acc = 1u;
           mma_commit(smem_u32(&bar_empty[stage]));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) mma_commit(smem_u32(&bar_tfull[buf]));
+        __syncwarp();
+        acc = 1u;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      if (ok && elect_one()) mma_commit(smem_u32(&bar_tfull[buf]));
+      __syncwarp();
     }
   } else {
     // ------------------------------------------------------------ epilogue (warps 2..5)
@@ -650,38 +658,43 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
       }
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc = idesc_tf32(128, BN, 1, 1);
-      constexpr uint32_t hi = desc_hi_mnmajor();
-      constexpr uint32_t step = 1024u >> 4;
-      const uint32_t a_lo0 = desc_lo_mnmajor(smem_base, C::kChunk), b_lo0 = desc_lo_mnmajor(smem_base + C::kABytes, C::kChunk);
-      int stage = 0;
-      uint32_t phase = 0;
-      int t = 0;
-      bool ok = true;
-      for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++t) {
-        const int split = unit % p.splits;
-        const int kb0 = split * p.kb_per_split;
-        const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
-        const int buf = t & 1;
-        const uint32_t use = (uint32_t)(t >> 1);
-        if (!mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 12)) { ok = false; break; }
+    // converged warp, elected issue (see tc_gemm_kernel)
+    constexpr uint32_t idesc = idesc_tf32(128, BN, 1, 1);
+    constexpr uint32_t hi = desc_hi_mnmajor();
+    constexpr uint32_t step = 1024u >> 4;
+    const uint32_t a_lo0 = desc_lo_mnmajor(smem_base, C::kChunk), b_lo0 = desc_lo_mnmajor(smem_base + C::kABytes, C::kChunk);
+    int stage = 0;
+    uint32_t phase = 0;
+    int t = 0;
+    bool ok = true;
+    for (int unit = blockIdx.x; unit < units && ok; unit += gridDim.x, ++t) {
+      const int split = unit % p.splits;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = kb0 + p.kb_per_split < p.kb_total ? kb0 + p.kb_per_split : p.kb_total;
+      const int buf = t & 1;
+      const uint32_t use = (uint32_t)(t >> 1);
+      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 12));
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t d_tmem = tmem_base + buf * BN;
+      uint32_t acc = 0;
+      for (int kb = kb0; kb < kb1; ++kb) {
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 13));
+        if (!ok) break;
         tc_fence_after();
-        const uint32_t d_tmem = tmem_base + buf * BN;
-        uint32_t acc = 0;
-        for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 13)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
+        const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
+        if (elect_one()) {
           mma_tf32_words(d_tmem, a_lo, hi, b_lo, hi, idesc, acc);
 #pragma unroll
           for (int kk = 1; kk < PB / 8; ++kk) mma_tf32_words(d_tmem, a_lo + kk * step, hi, b_lo + kk * step, hi, idesc, 1u);
-          acc = 1u;
           mma_commit(smem_u32(&bar_empty[stage]));
-          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
-        if (ok) mma_commit(smem_u32(&bar_tfull[buf]));
+        __syncwarp();
+        acc = 1u;
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
       }
+      if (ok && elect_one()) mma_commit(smem_u32(&bar_tfull[buf]));
+      __syncwarp();
     }
   } else {
     const int quarter = warp & 3;
@@ -801,7 +814,13 @@ WgradPlan wgrad_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int s
 long long mtb_tc_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
   if (cin % 32) return 0;
   WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
-  return (long long)q.splits * q.Kw * cout * 4 + 256;
+  long long bytes = (long long)q.splits * q.Kw * cout * 4 + 256;
+  const WgradRowsPlan rq = wgrad_rows_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  if (rq.ok) {
+    const long long b2 = (long long)rq.splits * q.Kw * cout * 4 + 256;
+    if (b2 > bytes) bytes = b2;
+  }
+  return bytes;
 }
 
 bool mtb_tc_conv2d_wgrad_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
@@ -817,6 +836,11 @@ bool mtb_tc_conv2d_wgrad_supported(int n, int cin, int h, int w, int kh, int kw,
 int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                             const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  const WgradRowsPlan rq = wgrad_rows_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+  if (rq.ok) {
+    MTB_REQUIRE(workspace && workspace_bytes >= (long long)rq.splits * kh * kw * cin * cout * 4, "conv2d_wgrad: workspace too small");
+    return run_wgrad_rows(rq, n, cin, h, w, kh, kw, ph, pw, cout, x, dy, dw, (float*)workspace, (cudaStream_t)stream);
+  }
   WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
   MTB_REQUIRE(workspace && workspace_bytes >= (long long)q.splits * q.Kw * cout * 4, "conv2d_wgrad: workspace too small");
   CUtensorMap mapX, mapDY;

@@ -114,7 +114,7 @@ class DataParallel:
     stream, so it overlaps the rest of backward and ``reduce_gradients()`` only waits for it.
     """
 
-    def __init__(self, module, process_group=None, buckets=2):
+    def __init__(self, module, process_group=None, buckets=1):
         import torch.distributed as dist
 
         self.module = module
