@@ -470,7 +470,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="profiling aid: run the step at another global batch (the benchmark configuration is 512)")
-    ap.add_argument("--grad-buckets", type=int, default=2,
+    ap.add_argument("--grad-buckets", type=int, default=1,
                     help="gradient all-reduce buckets (N>1): 1 = one all-reduce after backward, more = start each "
                          "bucket on a side stream as soon as backward has finished its gradients")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")

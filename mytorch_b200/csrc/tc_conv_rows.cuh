@@ -435,6 +435,7 @@ struct WgradRowsParams {
   int Wp, Hv, H, W, PH, PW, KH, KW;
   int Cin, Cout;
   int ncc_g;     // channel blocks of 32 per group
+  int n_tiles;   // output-channel tiles of BN
   int n_kwg;     // ceil(KW / 4)
   int splits, kb_total, kb_per_split;  // position blocks of 128
   uint32_t x_panel_bytes, y_panel_bytes, stage_bytes;
@@ -481,7 +482,9 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
   const uint32_t tmem_base = tmem_slot;
   volatile int* abort_ptr = &abort_flag;
 
-  const int group = blockIdx.x / p.splits, split = blockIdx.x - group * p.splits;
+  const int split = blockIdx.x % p.splits;
+  const int n0 = ((blockIdx.x / p.splits) % p.n_tiles) * BN;
+  const int group = blockIdx.x / (p.splits * p.n_tiles);
   const int cchunks = p.Cin / 32;
   const int cc0 = group * p.ncc_g;
   const int ncc = cchunks - cc0 < p.ncc_g ? cchunks - cc0 : p.ncc_g;
@@ -520,7 +523,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
           uint32_t dst = st + y_off;
           for (int r = 0; r < nr_y; ++r, dst += row_bytes) {
 #pragma unroll
-            for (int j = 0; j < BN / 32; ++j) tma_load_4d(dst + j * p.y_panel_bytes, &mapDY, full, j * 32, -p.PW, hr, im);
+            for (int j = 0; j < BN / 32; ++j) tma_load_4d(dst + j * p.y_panel_bytes, &mapDY, full, n0 + j * 32, -p.PW, hr, im);
             if (++hr == p.Hv) { hr = 0; ++im; }
           }
         }
@@ -592,14 +595,14 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
             const int kw = g * 4 + quarter;             // M block = tap within the group of four
             const int ci = (cc0 + c) * 32 + lane;
             const bool valid = kw < p.KW && ci < p.Cin;
-            float* orow = part + ((long long)(kh * p.KW + kw) * p.Cin + ci) * p.Cout;
+            float* orow = part + ((long long)(kh * p.KW + kw) * p.Cin + ci) * p.Cout + n0;
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
               uint32_t r[32];
               tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(a * BN + c0), r);
               tmem_ld_wait();
-              if (valid && c0 < p.Cout) {
-                if (vec_ok && c0 + 32 <= p.Cout) {
+              if (valid && n0 + c0 < p.Cout) {
+                if (vec_ok && n0 + c0 + 32 <= p.Cout) {
 #pragma unroll
                   for (int j = 0; j < 32; j += 4)
                     *reinterpret_cast<float4*>(orow + c0 + j) =
@@ -607,7 +610,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
                 } else {
 #pragma unroll
                   for (int j = 0; j < 32; ++j)
-                    if (c0 + j < p.Cout) orow[c0 + j] = __uint_as_float(r[j]);
+                    if (n0 + c0 + j < p.Cout) orow[c0 + j] = __uint_as_float(r[j]);
                 }
               }
             }
@@ -654,15 +657,18 @@ __global__ void __launch_bounds__(1024) wgrad_reduce_many_kernel(const float* __
 
 struct WgradRowsPlan {
   bool ok;
-  int bn, Wp, Hv, ncc_g, groups, n_kwg, splits, kb_total, kb_per_split;
+  int bn, n_tiles, Wp, Hv, ncc_g, groups, n_kwg, splits, kb_total, kb_per_split;
   uint32_t x_panel_bytes, y_panel_bytes, stage_bytes, smem_bytes;
 };
 
 WgradRowsPlan wgrad_rows_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
   WgradRowsPlan r{};
   if (getenv("MTB_DISABLE_ROWCONV") || getenv("MTB_DISABLE_ROWWGRAD")) return r;
-  if (sh != 1 || sw != 1 || kh != 2 * ph + 1 || kw != 2 * pw + 1 || kh * kw < 2 || pw > 7 || cin % 32 || cout > 128 || cout % 4) return r;
-  r.bn = cout <= 64 ? 64 : 128;
+  if (sh != 1 || sw != 1 || kh != 2 * ph + 1 || kw != 2 * pw + 1 || kh * kw < 2 || pw > 7 || cin % 32 || cout > 256 || cout % 4) return r;
+  // 64-wide output tiles: two channel blocks' accumulators fit in tensor memory side by side, so X
+  // and dY panels are each staged for 96 MMAs instead of 48
+  r.bn = (cout <= 64 || !getenv("MTB_WGRAD_BN128")) ? 64 : 128;
+  r.n_tiles = (cout + r.bn - 1) / r.bn;
   r.Wp = w + 2 * pw;
   r.Hv = h + ph;
   r.n_kwg = (kw + 3) / 4;
@@ -688,7 +694,7 @@ WgradRowsPlan wgrad_rows_plan(int n, int cin, int h, int w, int kh, int kw, int 
   r.smem_bytes = kWgRowsStages * r.stage_bytes + 1024;
   const long long Q = (long long)n * r.Hv * r.Wp;
   r.kb_total = (int)((Q + kWgRowsPB - 1) / kWgRowsPB);
-  int splits = mtb_sm_count() / r.groups;
+  int splits = mtb_sm_count() / (r.groups * r.n_tiles);
   if (splits < 1) splits = 1;
   if (splits > r.kb_total) splits = r.kb_total;
   r.kb_per_split = (r.kb_total + splits - 1) / splits;
@@ -720,11 +726,11 @@ int run_wgrad_rows(const WgradRowsPlan& q, int n, int cin, int h, int w, int kh,
   WgradRowsParams p{};
   p.Q = (long long)n * q.Hv * q.Wp;
   p.Wp = q.Wp; p.Hv = q.Hv; p.H = h; p.W = w; p.PH = ph; p.PW = pw; p.KH = kh; p.KW = kw;
-  p.Cin = cin; p.Cout = cout; p.ncc_g = q.ncc_g; p.n_kwg = q.n_kwg;
+  p.Cin = cin; p.Cout = cout; p.ncc_g = q.ncc_g; p.n_tiles = q.n_tiles; p.n_kwg = q.n_kwg;
   p.splits = q.splits; p.kb_total = q.kb_total; p.kb_per_split = q.kb_per_split;
   p.x_panel_bytes = q.x_panel_bytes; p.y_panel_bytes = q.y_panel_bytes; p.stage_bytes = q.stage_bytes;
   p.partial = partial;
-  const int grid = q.groups * q.splits;
+  const int grid = q.groups * q.n_tiles * q.splits;
   // straight-line MMA sequence when every CTA has the same, small number of channel blocks
   const int fix = (kh == 3 && q.n_kwg == 1 && (cin / 32) % q.ncc_g == 0 && q.ncc_g <= 2) ? q.ncc_g : 0;
   if (q.bn == 64) {

@@ -64,6 +64,16 @@ def test_conv_golden(g):
     (2, 32, 26, 26, 64, 3, 1, 0, True),
     (2, 3, 37, 41, 16, 7, 2, 3, False),
     (3, 20, 9, 11, 24, 3, 1, 1, True),
+    # stride-1 "same" filters on the row-staged kernels: odd image sizes, tiles that straddle images,
+    # partial channel blocks, 5x5 and 7x7 filters, more than two output-channel tiles, a row too wide
+    # for the row stage (falls back to the im2col kernels)
+    (3, 32, 17, 23, 40, 3, 1, 1, True),
+    (2, 64, 20, 36, 64, 5, 1, 2, False),
+    (2, 96, 24, 24, 72, 3, 1, 1, True),
+    (1, 64, 64, 64, 192, 3, 1, 1, False),
+    (4, 160, 16, 16, 128, 3, 1, 1, False),
+    (2, 32, 32, 32, 32, 7, 1, 3, False),
+    (1, 32, 40, 250, 32, 3, 1, 1, False),
 ])
 def test_conv_oracle(g, cfg):
     n, ci, h, w, co, k, s, p, bias = cfg
