@@ -84,10 +84,9 @@ __global__ void __launch_bounds__(256) bn_stats_partial_kernel(const float* __re
   }
 }
 
-// Thirty-two threads per channel: thread g merges partials g, g+32, ... in order (Chan's parallel
-// update), then the 32 results are merged in index order, so the result does not depend on
-// scheduling.  Writes the batch mean / biased variance, the per-channel scale
-// gamma/sqrt(var+eps) used by the normalise pass, and blends the running statistics.
+// Chan's parallel update of (count, mean, M2).  The finalise kernel below combines the per-CTA
+// partials with it and writes the batch mean / biased variance, the per-channel scale
+// gamma/sqrt(var+eps) used by the normalise pass, and the blended running statistics.
 __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, float nb, float mb, float qb) {
   if (nb == 0.f) return;
   float nt = n + nb;
@@ -101,32 +100,40 @@ __device__ __forceinline__ void chan_merge(float& n, float& mean, float& m2, flo
 __global__ void __launch_bounds__(1024) bn_stats_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma, float eps,
                                                                float one_minus_m, float m, float* running_mean, float* running_var,
                                                                float* __restrict__ mean_out, float* __restrict__ var_out, float* __restrict__ scale_out) {
-  // 32 channels x 32 partial-groups per CTA: consecutive threads read consecutive channels.
-  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + cx;
+  // 8 channels x 128 partial-groups per CTA.  Group g merges partials g, g+128, ... (all loads are
+  // issued before the first merge), then the 128 results are merged pairwise in a fixed tree, so the
+  // kernel is a couple of memory round trips long and the result does not depend on scheduling.
+  constexpr int G = 128, B = 5;
+  const int cx = threadIdx.x & 7, g = threadIdx.x >> 3;
+  const int c = blockIdx.x * 8 + cx;
   float n = 0.f, mean = 0.f, m2 = 0.f;
   if (c < C) {
-    int p = py;
-    for (; p + 96 < P; p += 128) {  // four independent loads in flight before the dependent merges
-      float v[4][3];
+    for (int p0 = g; p0 < P; p0 += G * B) {
+      float v[B][3];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const float* q = partial + (long long)(p + 32 * u) * 3 * C + c;
-        v[u][0] = q[0]; v[u][1] = q[C]; v[u][2] = q[2 * C];
+      for (int u = 0; u < B; ++u) {
+        const int p = p0 + G * u;
+        const float* q = partial + (long long)p * 3 * C + c;
+        const bool in = p < P;
+        v[u][0] = in ? q[0] : 0.f;
+        v[u][1] = in ? q[C] : 0.f;
+        v[u][2] = in ? q[2 * C] : 0.f;
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) chan_merge(n, mean, m2, v[u][0], v[u][1], v[u][2]);
-    }
-    for (; p < P; p += 32) {
-      const float* q = partial + (long long)p * 3 * C + c;
-      chan_merge(n, mean, m2, q[0], q[C], q[2 * C]);
+      for (int u = 0; u < B; ++u) chan_merge(n, mean, m2, v[u][0], v[u][1], v[u][2]);
     }
   }
-  __shared__ float sn[32][33], smean[32][33], sm2[32][33];
-  sn[py][cx] = n; smean[py][cx] = mean; sm2[py][cx] = m2;
-  __syncthreads();
-  if (py != 0 || c >= C) return;
-  for (int k = 1; k < 32; ++k) chan_merge(n, mean, m2, sn[k][cx], smean[k][cx], sm2[k][cx]);
+  __shared__ float sn[G][9], smean[G][9], sm2[G][9];
+  sn[g][cx] = n; smean[g][cx] = mean; sm2[g][cx] = m2;
+#pragma unroll
+  for (int s = G / 2; s >= 1; s >>= 1) {
+    __syncthreads();
+    if (g < s) {
+      chan_merge(n, mean, m2, sn[g + s][cx], smean[g + s][cx], sm2[g + s][cx]);
+      sn[g][cx] = n; smean[g][cx] = mean; sm2[g][cx] = m2;
+    }
+  }
+  if (g != 0 || c >= C) return;
   float mu = mean;
   float var = n > 0.f ? m2 / n : 0.f;
   mean_out[c] = mu;
@@ -243,21 +250,36 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
 __global__ void __launch_bounds__(1024) bn_bwd_final_kernel(const float* __restrict__ partial, int P, int C, const float* __restrict__ gamma,
                                                              const float* __restrict__ var, float eps, float inv_m, float* __restrict__ dgamma,
                                                              float* __restrict__ dbeta, float* __restrict__ coef) {
-  const int cx = threadIdx.x & 31, py = threadIdx.x >> 5;
-  const int c = blockIdx.x * 32 + cx;
+  // 8 channels x 128 partial-groups per CTA, loads first, then a fixed pairwise tree (see above).
+  constexpr int G = 128, B = 5;
+  const int cx = threadIdx.x & 7, g = threadIdx.x >> 3;
+  const int c = blockIdx.x * 8 + cx;
   float s0 = 0.f, s1 = 0.f;
   if (c < C) {
-#pragma unroll 4
-    for (int p = py; p < P; p += 32) {
-      s0 += partial[(long long)p * 2 * C + c];
-      s1 += partial[(long long)p * 2 * C + C + c];
+    for (int p0 = g; p0 < P; p0 += G * B) {
+      float v[B][2];
+#pragma unroll
+      for (int u = 0; u < B; ++u) {
+        const int p = p0 + G * u;
+        const bool in = p < P;
+        v[u][0] = in ? partial[(long long)p * 2 * C + c] : 0.f;
+        v[u][1] = in ? partial[(long long)p * 2 * C + C + c] : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < B; ++u) { s0 += v[u][0]; s1 += v[u][1]; }
     }
   }
-  __shared__ float t0[32][33], t1[32][33];
-  t0[py][cx] = s0; t1[py][cx] = s1;
-  __syncthreads();
-  if (py != 0 || c >= C) return;
-  for (int k = 1; k < 32; ++k) { s0 += t0[k][cx]; s1 += t1[k][cx]; }
+  __shared__ float t0[G][9], t1[G][9];
+  t0[g][cx] = s0; t1[g][cx] = s1;
+#pragma unroll
+  for (int s = G / 2; s >= 1; s >>= 1) {
+    __syncthreads();
+    if (g < s) {
+      s0 += t0[g + s][cx]; s1 += t1[g + s][cx];
+      t0[g][cx] = s0; t1[g][cx] = s1;
+    }
+  }
+  if (g != 0 || c >= C) return;
   float db = s0, dg = s1;
   if (dbeta) dbeta[c] = db;
   if (dgamma) dgamma[c] = dg;
@@ -350,7 +372,7 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
     if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
     MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
-    bn_stats_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+    bn_stats_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
                                                       running_mean, running_var, mean, var, scale);
     MTB_LAUNCH_CHECK("bn_stats_final_kernel");
   } else {
@@ -391,7 +413,7 @@ MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const floa
   else { if (relu) MTB_BN_PARTIAL(1, true); else MTB_BN_PARTIAL(1, false); }
 #undef MTB_BN_PARTIAL
   MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
-  bn_bwd_final_kernel<<<mtb_div_up(c, 32), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+  bn_bwd_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
                                                           dgamma, dbeta, coef);
   MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
   ColCfg s = stream_cfg(rows, c, aligned);
