@@ -44,6 +44,12 @@ int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh,
 /* dx[N,H,W,Cin]: every element is written (zeros where no window reaches); no atomics */
 int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                          const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream);
+/* dx = data gradient + addend (addend: same shape as dx, not aliasing it): gradient accumulation for
+ * a tensor with a second consumer, fused into the convolution's epilogue where the kernel allows.
+ * No counterpart in the reference, whose tape adds the two gradients with a separate `add`
+ * (mytorch/autograd.py:160-170). */
+int mtb_conv2d_dgrad_add_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                             const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream);
 /* dw[Cout,KH,KW,Cin]; split-K partials go to workspace and are summed in a fixed order */
 int mtb_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                          const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream);

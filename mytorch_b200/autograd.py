@@ -39,6 +39,10 @@ class DAGTracker:
         # optional callback(tensor): a leaf tensor has received its last gradient contribution of
         # the running backward pass (used to start gradient all-reduces while backward continues)
         self.leaf_grad_final_hook = None
+        # operator name -> index of the input whose already accumulated gradient the operator's
+        # backward can add itself (keyword ``accumulate_dx``); the tape then stores the returned
+        # gradient instead of launching an add
+        self.fused_accumulate = {}
 
     def register_backward_function(self, op_name):
         def decorator(func):
@@ -91,13 +95,22 @@ class DAGTracker:
 
         for node in order:
             func = self._backward_funcs[node.name]
-            grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs))
+            fused = None  # the input whose gradient so far is handed to the operator
+            slot = self.fused_accumulate.get(node.name)
+            if slot is not None:
+                cand = node.inputs[slot]
+                if isinstance(cand, Tensor) and cand.requires_grad and cand.grad is not None:
+                    fused = cand
+            if fused is not None:
+                grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs, accumulate_dx=fused.grad))
+            else:
+                grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs))
             grads += [None] * (len(node.inputs) - len(grads))
             for arg, grad in zip(node.inputs, grads):
                 if arg is None or not isinstance(arg, Tensor) or not arg.requires_grad:
                     continue
                 if grad is not None:
-                    if arg.grad is None:
+                    if arg.grad is None or (arg is fused and grad is grads[slot]):
                         arg.grad = grad
                     else:
                         if arg.grad.shape != grad.shape:

@@ -185,7 +185,10 @@ def cuda_conv2d(input, weight, bias, stride, padding):
 
 
 @_reg("cuda", "conv2d_backward")
-def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding):
+def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None):
+    """``accumulate_dx``: a gradient the input has already received from another consumer; when given,
+    the returned dx is the data gradient PLUS that tensor (added in the convolution's epilogue where
+    the kernel allows), and the caller stores it instead of adding the two itself."""
     _f32(output_grad, input, weight)
     env = _env(input)
     want_dx, want_dw, cin = input.requires_grad, weight.requires_grad, input.shape[1]
@@ -198,9 +201,14 @@ def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding):
     dx = dw = db = None
     if want_dx:
         dx = _new(input.shape, input)
-        env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(dx), ws, ws_bytes, st)
-        if padded:
-            dx = _take_channels(env, dx, cin, dx)
+        if accumulate_dx is not None and not padded:
+            env.lib.conv2d_dgrad_add_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(accumulate_dx), _ptr(dx), ws, ws_bytes, st)
+        else:
+            env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(dx), ws, ws_bytes, st)
+            if padded:
+                dx = _take_channels(env, dx, cin, dx)
+            if accumulate_dx is not None:
+                dx = BackendDispatcher.instance().dispatch("cuda", "add")(dx, accumulate_dx, 1)
     if want_dw:
         dw = _new(weight.shape, weight)
         env.lib.conv2d_wgrad_f32(*a, _ptr(input), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)

@@ -37,6 +37,7 @@ struct RowConvParams {
   float* out;
   long long ldo;
   const float* bias;
+  const float* addend;     // optional [same shape as out]: out = conv + addend (gradient accumulation)
   int relu;
   int b_tap_x[64];         // MN-major B only: first column of tap j in the weight matrix
 };
@@ -257,7 +258,8 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     // ------------------------------------------------------------ epilogue (warps 2..5)
     const int quarter = warp & 3;
     int t = 0;
-    const bool vec_ok = (p.ldo % 4 == 0) && (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias)) & 15u) == 0);
+    const bool vec_ok = (p.ldo % 4 == 0) &&
+                        (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.addend)) & 15u) == 0);
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
       const long long q = (long long)(tile / p.n_tiles) * 128 + quarter * 32 + lane;
       const int n0 = (tile % p.n_tiles) * BN;
@@ -269,12 +271,24 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       const long long img = v / p.Hv;
       const int hrow = (int)(v - img * p.Hv);
       const bool valid = q < p.Q && hrow < p.H && wp >= p.PW && wp < p.W + p.PW;
-      float* orow = p.out + ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
+      const long long ooff = ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
+      float* orow = p.out + ooff;
+      const float* arow = p.addend ? p.addend + ooff : nullptr;
+      // the addend row is fetched while the MMAs of this tile still run: loading it after the
+      // accumulator is ready would put a memory round trip per 32 columns into the epilogue,
+      // which then takes longer than the main loop of a tile
+      constexpr int kPre = BN <= 128 ? BN / 4 : 1;
+      float4 pre[kPre];
+      const bool prefetched = BN <= 128 && arow != nullptr && valid && vec_ok && n0 + BN <= p.N;
+      if (prefetched) {
+#pragma unroll
+        for (int j = 0; j < kPre; ++j) pre[j] = __ldg(reinterpret_cast<const float4*>(arow + n0) + j);
+      }
       bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 16);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
-#pragma unroll 1
+#pragma unroll
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
         tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
@@ -289,6 +303,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
                 o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
               }
+              if (arow) {
+                const float4 b = prefetched ? pre[BN <= 128 ? (c0 + j) / 4 : 0] : *reinterpret_cast<const float4*>(arow + col0 + j);
+                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+              }
               if (p.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
               *reinterpret_cast<float4*>(orow + col0 + j) = o;
             }
@@ -298,6 +316,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               if (col0 + j < p.N) {
                 float o = __uint_as_float(r[j]);
                 if (p.bias) o += p.bias[col0 + j];
+                if (arow) o += arow[col0 + j];
                 if (p.relu) o = fmaxf(o, 0.f);
                 orow[col0 + j] = o;
               }
@@ -395,7 +414,7 @@ int launch_row_conv_bn(int bn, const CUtensorMap& mapA, const CUtensorMap& mapB,
 // act: [N, H, W, kc] channels-last; out: [N, H, W, nout].
 template <int BMODE>
 int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, int kh, int kw, int ph, int pw, int nout, const float* act,
-                 const CUtensorMap& mapB, const int* b_tap_x, const float* bias, int relu, float* out, cudaStream_t st) {
+                 const CUtensorMap& mapB, const int* b_tap_x, const float* bias, const float* addend, int relu, float* out, cudaStream_t st) {
   CUtensorMap mapA;
   int rc = tc::encode_rows_4d(&mapA, act, n, h, w, kc, 32, plan.Wp);
   if (rc) return rc;
@@ -405,7 +424,7 @@ int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, i
   p.cchunks = kc / 32; p.kc_total = kc; p.N = nout;
   p.m_tiles = (int)((p.Q + 127) / 128); p.n_tiles = (nout + bn - 1) / bn;
   p.a_stage_bytes = plan.a_stage_bytes; p.b_stages = plan.b_stages; p.tps = plan.tps; p.resident = plan.resident;
-  p.out = out; p.ldo = nout; p.bias = bias; p.relu = relu;
+  p.out = out; p.ldo = nout; p.bias = bias; p.addend = addend; p.relu = relu;
   if (b_tap_x) for (int j = 0; j < kh * kw; ++j) p.b_tap_x[j] = b_tap_x[j];
   return launch_row_conv_bn<BMODE>(bn, mapA, mapB, p, plan.smem_bytes, st);
 }

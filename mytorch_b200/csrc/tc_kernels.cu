@@ -445,7 +445,7 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
   if (rc) return rc;
   const RowConvPlan plan = row_conv_plan(h, w, kh, kw, sh, sw, ph, pw, cin, cout, bn);
-  if (plan.ok) return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, relu, y, (cudaStream_t)stream);
+  if (plan.ok) return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, nullptr, relu, y, (cudaStream_t)stream);
   rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
   if (rc) return rc;
   GemmParams p{};
@@ -476,8 +476,10 @@ bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw,
 // are output channels = the reduction index, columns are input channels), and the epilogue
 // scatters rows to the class's pixels.  Classes without taps (stride larger than the filter)
 // receive zeros.  No atomics; every element of dX is written exactly once.
+// addend (may be NULL): dx = dgrad + addend.  Fused into the epilogue on the row-staged path; the
+// other paths write dgrad and add afterwards.
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
-                            const float* wt, float* dx, void*, long long, void* stream) {
+                            const float* wt, const float* addend, float* dx, void*, long long, void* stream) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   const int bn = pick_bn_for(cin, (long long)n * h * w / (sh * sw));
   cudaStream_t st = (cudaStream_t)stream;
@@ -490,7 +492,7 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
     int tap_x[64];
     for (int jh = 0; jh < kh; ++jh)
       for (int jw = 0; jw < kw; ++jw) tap_x[jh * kw + jw] = ((kh - 1 - jh) * kw + (kw - 1 - jw)) * cin;
-    return run_row_conv<B_MNMAJOR>(plan, bn, n, h, w, cout, kh, kw, ph, pw, cin, dy, mapB, tap_x, nullptr, 0, dx, st);
+    return run_row_conv<B_MNMAJOR>(plan, bn, n, h, w, cout, kh, kw, ph, pw, cin, dy, mapB, tap_x, nullptr, addend, 0, dx, st);
   }
   struct Axis { int taps, start, count, lower, upper; };
   auto axis = [](int a, int size, int osize, int k, int s, int pad) {
@@ -535,6 +537,7 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
       if (rc) return rc;
     }
   }
+  if (addend) return mtb_add_f32(dx, addend, dx, (long long)n * h * w * cin, 1.0f, st);
   return MTB_OK;
 }
 

@@ -17,6 +17,15 @@ def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0) -> Ten
 
 
 @tracker.register_backward_function("conv2d")
-def conv2d_backward(output_grad, input, weight, bias, stride, padding):
-    dx, dw, db = dispatch(input.device, "conv2d_backward")(output_grad, input, weight, bias, stride, padding)
+def conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None):
+    """``accumulate_dx`` is the gradient ``input`` already holds (the tape passes it for operators
+    listed in ``DAGTracker.fused_accumulate``): the returned dx then includes it."""
+    backend = dispatch(input.device, "conv2d_backward")
+    if accumulate_dx is not None:
+        dx, dw, db = backend(output_grad, input, weight, bias, stride, padding, accumulate_dx=accumulate_dx)
+    else:
+        dx, dw, db = backend(output_grad, input, weight, bias, stride, padding)
     return [dx, dw, db]
+
+
+tracker.fused_accumulate["conv2d"] = 0  # input 0's accumulated gradient can be folded into the backward

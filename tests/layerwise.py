@@ -68,14 +68,15 @@ class LayerwiseChecker:
 
     # ---- backward: wraps every registered backward function
     def _backward(self, name, func):
-        def wrapped(*args):
-            grads = func(*args)
+        def wrapped(*args, **kwargs):
+            grads = func(*args, **kwargs)
             g = [_h(t) if t is not None and hasattr(t, "shape") else None for t in grads]
             if name == "conv2d":
                 dy, x, w, b, s, p = args
                 rdx, rdw, rdb = O.conv2d_backward(_h(dy), _h(x.detach()), _h(w.detach()), b is not None, s, p)
                 if g[0] is not None:
-                    self._note("bwd", name + ".dx", g[0], rdx, TF32_TOL)
+                    acc = kwargs.get("accumulate_dx")  # the returned dx then includes this earlier gradient
+                    self._note("bwd", name + ".dx", g[0], rdx if acc is None else rdx + _h(acc), TF32_TOL)
                 self._note("bwd", name + ".dw", g[1], rdw, TF32_TOL)
                 if b is not None:
                     self._note("bwd", name + ".db", g[2], rdb, FP32_TOL * 5)

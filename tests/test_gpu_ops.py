@@ -86,6 +86,24 @@ def test_conv_oracle(g, cfg):
     _conv_check(g, x, wt, b, dy, s, p)
 
 
+@pytest.mark.parametrize("cfg", [(8, 64, 32, 32, 64, 3, 1, 1), (8, 64, 32, 32, 128, 3, 2, 1), (2, 20, 9, 11, 24, 3, 1, 1), (8, 3, 32, 32, 64, 3, 1, 1)])
+def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
+    """dx returned with ``accumulate_dx`` equals dgrad + that tensor bit for bit, on the row-staged
+    path (sum in the epilogue), the im2col path, the CUDA-core path and the channel-padded stem."""
+    n, ci, h, w, co, k, s, p = cfg
+    rng = np.random.default_rng(11)
+    x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    wt = rng.standard_normal((co, ci, k, k)).astype(np.float32)
+    oh, ow = O.conv_out_hw(h, w, k, k, s, p)
+    dy = rng.standard_normal((n, co, oh, ow)).astype(np.float32)
+    prev = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    xt, wtt, dyt, pt = g.dev(x, True), g.dev(wt, True), g.dev(dy), g.dev(prev)
+    dx, _, _ = g.op("conv2d_backward")(dyt, xt, wtt, None, (s, s), (p, p))
+    both, _, _ = g.op("conv2d_backward")(dyt, xt, wtt, None, (s, s), (p, p), accumulate_dx=pt)
+    assert np.array_equal(g.host(both), g.host(dx) + prev)
+    assert np.array_equal(g.host(pt), prev)
+
+
 def test_conv_is_deterministic(g):
     rng = np.random.default_rng(5)
     x = rng.standard_normal((8, 64, 16, 16)).astype(np.float32)

@@ -99,6 +99,63 @@ def test_backward_requires_graph_and_scalar():
     assert not DAGTracker.instance().no_grad
 
 
+def test_tape_hands_accumulated_gradient_to_operators_that_can_add_it():
+    """An operator listed in ``fused_accumulate`` receives the gradient its input already holds and
+    returns the sum; the tape stores that instead of adding.  Leaves receive their last gradient
+    exactly once through the hook, whatever the number of consumers."""
+    from mytorch_b200.autograd import DAGTracker
+    from mytorch_b200.ops._common import record
+
+    tr = DAGTracker.instance()
+    seen = []
+
+    def scale_op(name, x, k):
+        out = mt.tensor(x._numpy() * np.float32(k))
+        out.requires_grad = True
+        return record(name, [x, k], out)
+
+    def total(x):  # a one-element tensor to call backward on
+        out = mt.tensor(np.array([x._numpy().sum()], np.float32))
+        out.requires_grad = True
+        return record("t_sum", [x], out)
+
+    @tr.register_backward_function("t_sum")
+    def _(dy, x):
+        return [mt.tensor(np.full(x.shape, dy._numpy()[0], np.float32))]
+
+    @tr.register_backward_function("t_plain")
+    def _(dy, x, k):
+        return [mt.tensor(dy._numpy() * np.float32(k)), None]
+
+    @tr.register_backward_function("t_fused")
+    def _(dy, x, k, accumulate_dx=None):
+        seen.append(None if accumulate_dx is None else accumulate_dx._numpy().copy())
+        g = dy._numpy() * np.float32(k)
+        return [mt.tensor(g if accumulate_dx is None else g + accumulate_dx._numpy()), None]
+
+    @tr.register_backward_function("t_add")
+    def _(dy, a, b):
+        return [dy, dy]
+
+    tr.fused_accumulate["t_fused"] = 0
+    finals = []
+    tr.leaf_grad_final_hook = lambda t: finals.append(id(t))
+    try:
+        x = mt.tensor(np.arange(4, dtype=np.float32), requires_grad=True)
+        a = scale_op("t_fused", x, 2.0)      # created first, so its backward runs last
+        b = scale_op("t_plain", x, 3.0)
+        s = mt.tensor(a._numpy() + b._numpy())
+        s.requires_grad = True
+        record("t_add", [a, b], s)
+        total(s).backward()
+    finally:
+        tr.leaf_grad_final_hook = None
+        del tr.fused_accumulate["t_fused"]
+    assert len(seen) == 1 and np.array_equal(seen[0], np.full(4, 3.0, np.float32))   # got the gradient from t_plain
+    assert np.array_equal(x.grad._numpy(), np.full(4, 5.0, np.float32))
+    assert finals == [id(x)]
+
+
 def _declared_symbols():
     text = open(os.path.join(ROOT, "include", "mytorch_b200.h")).read()
     return sorted(set(re.findall(r"\b(mtb_[a-z0-9_]+)\s*\(", text)))
