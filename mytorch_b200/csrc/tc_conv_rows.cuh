@@ -50,7 +50,10 @@ constexpr int kRowAStages = 2;
 // work, and a tcgen05.mma takes ~45 cycles to issue whatever its width, so a stage of 4 narrow
 // MMAs (192 cycles of work at N = 64) leaves the tensor core idle most of the time.  With all
 // nine taps of a 3x3 filter in one stage (36 MMAs) the hand-over is amortised.
-template <int BN, int BMODE, int FK>
+// MT = tiles of 128 positions per work item.  With streamed weights two tiles share every weight
+// stage (two accumulators), which halves the L2 -> shared-memory weight traffic per MMA; that traffic,
+// at ~47 B/cycle/SM, is what bounds the 128-channel layers.
+template <int BN, int BMODE, int FK, int MT>
 __global__ void __launch_bounds__(192, 1)
 tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const RowConvParams p) {
   constexpr uint32_t kTapBytes = BN * 128;
@@ -89,7 +92,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     fence_barrier_init();
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&tmem_slot), 2 * BN);
+    tmem_alloc(smem_u32(&tmem_slot), 2 * MT * BN);
     tmem_relinquish();
   }
   fence_proxy_async();
@@ -97,7 +100,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int tiles = ((p.m_tiles + MT - 1) / MT) * p.n_tiles;  // work items
   const int taps = p.KH * p.KW;
   volatile int* abort_ptr = &abort_flag;
 
@@ -126,10 +129,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           }
       }
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const long long q0 = (long long)(tile / p.n_tiles) * 128;
+        const long long q0 = (long long)(tile / p.n_tiles) * (128 * MT);
         const int n0 = (tile % p.n_tiles) * BN;
         const int v_lo = (int)(q0 / p.Wp) - p.PH;
-        const int nr = (int)((q0 + 127) / p.Wp) + p.PH - v_lo + 1;
+        const int nr = (int)((q0 + 128 * MT - 1) / p.Wp) + p.PH - v_lo + 1;
         // first image row: floor division (v_lo is -PH for the very first tile)
         const int img = v_lo >= 0 ? v_lo / p.Hv : -1;
         const int hrow = v_lo - img * p.Hv;
@@ -182,14 +185,15 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     bool ok = true;
     if (p.resident && blockIdx.x < tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bres), 0, abort_ptr, 17));
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
-      const long long q0 = (long long)(tile / p.n_tiles) * 128;
+      const long long q0 = (long long)(tile / p.n_tiles) * (128 * MT);
       const int col = (int)(q0 % p.Wp);
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 13));
       if (!ok) break;
       tc_fence_after();
-      const uint32_t d_tmem = tmem_base + buf * BN;
+      const uint32_t d_tmem = tmem_base + buf * (MT * BN);
+      constexpr uint32_t tile_step = 128u * 8u;  // the next tile's positions start 128 pixels (of 8 units) further
       for (int cc = 0; cc < p.cchunks && ok; ++cc) {
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_afull[as]), aphase, abort_ptr, 14));
         if (!ok) break;
@@ -207,20 +211,49 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
                 for (int kw = 0; kw < 3; ++kw)
 #pragma unroll
                   for (int k = 0; k < 4; ++k)
-                    mma_tf32_words(d_tmem, a_tile + kh * row_step + kw * 8 + 2 * k, a_hi, b_cc + (kh * 3 + kw) * tap_step + k * b_step, b_hi, idesc,
-                                   (kh + kw + k) ? 1u : (uint32_t)(cc > 0));
+#pragma unroll
+                    for (int m = 0; m < MT; ++m)
+                      mma_tf32_words(d_tmem + m * BN, a_tile + m * tile_step + kh * row_step + kw * 8 + 2 * k, a_hi,
+                                     b_cc + (kh * 3 + kw) * tap_step + k * b_step, b_hi, idesc, (kh + kw + k) ? 1u : (uint32_t)(cc > 0));
             } else {
               uint32_t a_row = a_tile, a_lo = a_tile, b_lo = b_cc;
               int kw = 0;
               for (int tap = 0; tap < taps; ++tap, b_lo += tap_step) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) mma_tf32_words(d_tmem, a_lo + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc, (tap + k) ? 1u : (uint32_t)(cc > 0));
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                  for (int m = 0; m < MT; ++m)
+                    mma_tf32_words(d_tmem + m * BN, a_lo + m * tile_step + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc, (tap + k) ? 1u : (uint32_t)(cc > 0));
                 a_lo += 8u;
                 if (++kw == p.KW) { kw = 0; a_row += row_step; a_lo = a_row; }
               }
             }
             mma_commit(smem_u32(&bar_aempty[as]));
           }
+          __syncwarp();
+        } else if (FK == 3) {
+          // streamed weights, 3x3 filter: one filter row (3 taps) per weight stage, straight-line issue
+#pragma unroll
+          for (int kh = 0; kh < 3; ++kh) {
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), bphase, abort_ptr, 15));
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t b_row = b_lo0 + bs * (b_stage_bytes >> 4);
+            if (elect_one()) {
+#pragma unroll
+              for (int kw = 0; kw < 3; ++kw)
+#pragma unroll
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                  for (int m = 0; m < MT; ++m)
+                    mma_tf32_words(d_tmem + m * BN, a_tile + m * tile_step + kh * row_step + kw * 8 + 2 * k, a_hi, b_row + kw * tap_step + k * b_step,
+                                   b_hi, idesc, (kh + kw + k) ? 1u : (uint32_t)(cc > 0));
+              mma_commit(smem_u32(&bar_bempty[bs]));
+            }
+            __syncwarp();
+            if (++bs == BST) { bs = 0; bphase ^= 1u; }
+          }
+          if (ok && elect_one()) mma_commit(smem_u32(&bar_aempty[as]));
           __syncwarp();
         } else {
           int kh = 0, kw = 0;
@@ -235,7 +268,11 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               int w = kw;
               for (int j = 0; j < cnt; ++j, b_lo += tap_step) {
 #pragma unroll
-                for (int k = 0; k < 4; ++k) mma_tf32_words(d_tmem, a_lo + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc, (tap0 + j + k) ? 1u : (uint32_t)(cc > 0));
+                for (int k = 0; k < 4; ++k)
+#pragma unroll
+                  for (int m = 0; m < MT; ++m)
+                    mma_tf32_words(d_tmem + m * BN, a_lo + m * tile_step + 2 * k, a_hi, b_lo + k * b_step, b_hi, idesc,
+                                   (tap0 + j + k) ? 1u : (uint32_t)(cc > 0));
                 a_lo += 8u;
                 if (++w == p.KW) { w = 0; a_lo += row_step - (uint32_t)p.KW * 8u; }
               }
@@ -261,64 +298,73 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const bool vec_ok = (p.ldo % 4 == 0) &&
                         (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.addend)) & 15u) == 0);
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
-      const long long q = (long long)(tile / p.n_tiles) * 128 + quarter * 32 + lane;
+      const long long q_item = (long long)(tile / p.n_tiles) * (128 * MT) + quarter * 32 + lane;
       const int n0 = (tile % p.n_tiles) * BN;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       // position -> pixel; padding columns and separator rows have no output
-      const long long v = q / p.Wp;
-      const int wp = (int)(q - v * p.Wp);
-      const long long img = v / p.Hv;
-      const int hrow = (int)(v - img * p.Hv);
-      const bool valid = q < p.Q && hrow < p.H && wp >= p.PW && wp < p.W + p.PW;
-      const long long ooff = ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
-      float* orow = p.out + ooff;
-      const float* arow = p.addend ? p.addend + ooff : nullptr;
-      // the addend row is fetched while the MMAs of this tile still run: loading it after the
-      // accumulator is ready would put a memory round trip per 32 columns into the epilogue,
-      // which then takes longer than the main loop of a tile
-      constexpr int kPre = BN <= 128 ? BN / 4 : 1;
+      long long ooff[MT];
+      bool valid[MT];
+#pragma unroll
+      for (int m = 0; m < MT; ++m) {
+        const long long q = q_item + 128 * m;
+        const long long v = q / p.Wp;
+        const int wp = (int)(q - v * p.Wp);
+        const long long img = v / p.Hv;
+        const int hrow = (int)(v - img * p.Hv);
+        valid[m] = q < p.Q && hrow < p.H && wp >= p.PW && wp < p.W + p.PW;
+        ooff[m] = ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
+      }
+      // With one tile per item the addend row is fetched while the MMAs of this tile still run:
+      // loading it after the accumulator is ready would put a memory round trip per 32 columns
+      // into the epilogue, which then takes longer than the main loop of a tile.
+      constexpr int kPre = (MT == 1 && BN <= 128) ? BN / 4 : 1;
       float4 pre[kPre];
-      const bool prefetched = BN <= 128 && arow != nullptr && valid && vec_ok && n0 + BN <= p.N;
+      const bool prefetched = MT == 1 && BN <= 128 && p.addend != nullptr && valid[0] && vec_ok && n0 + BN <= p.N;
       if (prefetched) {
 #pragma unroll
-        for (int j = 0; j < kPre; ++j) pre[j] = __ldg(reinterpret_cast<const float4*>(arow + n0) + j);
+        for (int j = 0; j < kPre; ++j) pre[j] = __ldg(reinterpret_cast<const float4*>(p.addend + ooff[0] + n0) + j);
       }
       bool ok = lane != 0 || mbar_wait(smem_u32(&bar_tfull[buf]), use & 1u, abort_ptr, 16);
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-        tmem_ld_wait();
-        const int col0 = n0 + c0;
-        if (valid && col0 < p.N) {
-          if (vec_ok && col0 + 32 <= p.N) {
+      for (int m = 0; m < MT; ++m) {
+        float* orow = p.out + ooff[m];
+        const float* arow = p.addend ? p.addend + ooff[m] : nullptr;
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (p.bias) {
-                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-              }
-              if (arow) {
-                const float4 b = prefetched ? pre[BN <= 128 ? (c0 + j) / 4 : 0] : *reinterpret_cast<const float4*>(arow + col0 + j);
-                o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-              }
-              if (p.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
-              *reinterpret_cast<float4*>(orow + col0 + j) = o;
-            }
-          } else {
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf * MT + m) * BN + c0), r);
+          tmem_ld_wait();
+          const int col0 = n0 + c0;
+          if (valid[m] && col0 < p.N) {
+            if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.N) {
-                float o = __uint_as_float(r[j]);
-                if (p.bias) o += p.bias[col0 + j];
-                if (arow) o += arow[col0 + j];
-                if (p.relu) o = fmaxf(o, 0.f);
-                orow[col0 + j] = o;
+              for (int j = 0; j < 32; j += 4) {
+                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (p.bias) {
+                  const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                }
+                if (arow) {
+                  const float4 b = prefetched ? pre[kPre > 1 ? (c0 + j) / 4 : 0] : *reinterpret_cast<const float4*>(arow + col0 + j);
+                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+                }
+                if (p.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
+                *reinterpret_cast<float4*>(orow + col0 + j) = o;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float o = __uint_as_float(r[j]);
+                  if (p.bias) o += p.bias[col0 + j];
+                  if (arow) o += arow[col0 + j];
+                  if (p.relu) o = fmaxf(o, 0.f);
+                  orow[col0 + j] = o;
+                }
               }
             }
           }
@@ -338,7 +384,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   }
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, 2 * MT * BN);
   }
 }
 
@@ -346,11 +392,42 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
 // handles or when too much of the work would land on padding.
 struct RowConvPlan {
   bool ok;
-  int Wp, Hv, nr_max, b_stages, tps, resident;
+  int Wp, Hv, nr_max, b_stages, tps, resident, mt;
   uint32_t a_stage_bytes, smem_bytes;
 };
 
-RowConvPlan row_conv_plan(int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int kc, int nout, int bn) {
+// One candidate layout: mt tiles per work item.
+static bool row_conv_layout(RowConvPlan& r, int mt, int ph, int pw, int taps, int kc, int nout, int bn, bool allow_resident) {
+  r.mt = mt;
+  r.nr_max = (r.Wp - 1 + 128 * mt - 1) / r.Wp + 1 + 2 * ph;
+  const uint32_t need = kRowLead + (uint32_t)(r.nr_max * r.Wp + pw + 8) * 128u;
+  r.a_stage_bytes = (need + 1023u) & ~1023u;
+  const uint32_t budget = 227u * 1024u - 2048u;
+  const uint32_t fixed = 1024u + kRowAStages * r.a_stage_bytes;
+  const uint32_t tap_bytes = (uint32_t)bn * 128u;
+  if (fixed + 3u * tap_bytes > budget) return false;
+  const uint32_t filter_bytes = (uint32_t)taps * (kc / 32) * tap_bytes;
+  r.resident = 0;
+  if (allow_resident && nout <= bn && fixed + filter_bytes <= budget) {  // the whole filter fits beside the activation ring
+    r.resident = 1;
+    r.tps = taps;
+    r.b_stages = 1;
+    r.smem_bytes = fixed + filter_bytes;
+    return true;
+  }
+  // the most taps per weight stage that still leaves two stages (hand-overs are expensive)
+  int tps = (int)((budget - fixed) / (2u * tap_bytes));
+  if (tps > taps) tps = taps;
+  if (bn >= 256 || tps < 2) tps = 1;  // N = 256: four MMAs already outlast a hand-over
+  if (taps == 9 && tps >= 3) tps = 3;  // 3x3: one filter row per stage, which the unrolled issue path expects
+  r.tps = tps;
+  int bst = (int)((budget - fixed) / (tps * tap_bytes));
+  r.b_stages = bst > 8 ? 8 : bst;
+  r.smem_bytes = fixed + r.b_stages * tps * tap_bytes;
+  return true;
+}
+
+RowConvPlan row_conv_plan(int n, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int kc, int nout, int bn) {
   RowConvPlan r{};
   if (getenv("MTB_DISABLE_ROWCONV")) return r;
   if (sh != 1 || sw != 1 || kh != 2 * ph + 1 || kw != 2 * pw + 1 || kh * kw < 2 || kh * kw > 64 || pw > 7 || kc % 32) return r;
@@ -358,56 +435,45 @@ RowConvPlan row_conv_plan(int h, int w, int kh, int kw, int sh, int sw, int ph, 
   r.Hv = h + ph;
   if (r.Wp > 256) return r;
   if ((double)w * h < 0.8 * (double)r.Wp * r.Hv) return r;  // too much padding: the im2col kernel wastes nothing
-  r.nr_max = (r.Wp - 1 + 127) / r.Wp + 1 + 2 * ph;
-  const uint32_t need = kRowLead + (uint32_t)(r.nr_max * r.Wp + pw + 8) * 128u;
-  r.a_stage_bytes = (need + 1023u) & ~1023u;
-  const uint32_t budget = 227u * 1024u - 2048u;
-  const uint32_t fixed = 1024u + kRowAStages * r.a_stage_bytes;
-  const uint32_t tap_bytes = (uint32_t)bn * 128u;
-  if (fixed + 3u * tap_bytes > budget) return r;
   const int taps = kh * kw;
-  const uint32_t filter_bytes = (uint32_t)taps * (kc / 32) * tap_bytes;
-  if (nout <= bn && fixed + filter_bytes <= budget) {  // the whole filter fits beside the activation ring
-    r.resident = 1;
-    r.tps = taps;
-    r.b_stages = 1;
-    r.smem_bytes = fixed + filter_bytes;
-    r.ok = true;
-    return r;
-  }
-  // the most taps per weight stage that still leaves two stages (hand-overs are expensive)
-  int tps = (int)((budget - fixed) / (2u * tap_bytes));
-  if (tps > taps) tps = taps;
-  if (bn >= 256 || tps < 2) tps = 1;  // N = 256: four MMAs already outlast a hand-over
-  r.tps = tps;
-  int bst = (int)((budget - fixed) / (tps * tap_bytes));
-  r.b_stages = bst > 8 ? 8 : bst;
-  r.smem_bytes = fixed + r.b_stages * tps * tap_bytes;
+  if (!row_conv_layout(r, 1, ph, pw, taps, kc, nout, bn, true)) return r;
   r.ok = true;
+  // Streamed weights: let two tiles share every weight stage when that still fills the GPU.
+  if (!r.resident && bn <= 128 && !getenv("MTB_ROWCONV_MT1")) {
+    const long long items = (((long long)n * r.Hv * r.Wp + 255) / 256) * ((nout + bn - 1) / bn);
+    RowConvPlan r2 = r;
+    const long long min_items = getenv("MTB_ROWCONV_MIN_ITEMS") ? atoll(getenv("MTB_ROWCONV_MIN_ITEMS")) : 2LL * mtb_sm_count();
+    if (items >= min_items && row_conv_layout(r2, 2, ph, pw, taps, kc, nout, bn, false) && r2.tps >= 2) r = r2;
+  }
   return r;
 }
 
-template <int BN, int BMODE, int FK>
+template <int BN, int BMODE, int FK, int MT>
 int launch_row_conv(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
-  auto kernel = tc_conv_rows_kernel<BN, BMODE, FK>;
+  auto kernel = tc_conv_rows_kernel<BN, BMODE, FK, MT>;
   static bool configured = false;
   if (!configured) {
     MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
     configured = true;
   }
-  const int tiles = p.m_tiles * p.n_tiles;
-  const int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
+  const int items = ((p.m_tiles + MT - 1) / MT) * p.n_tiles;
+  const int grid = items < mtb_sm_count() ? items : mtb_sm_count();
   kernel<<<grid, 192, smem_bytes, st>>>(mapA, mapB, p);
   MTB_LAUNCH_CHECK("tc_conv_rows_kernel");
   return MTB_OK;
 }
 
 template <int BMODE>
-int launch_row_conv_bn(int bn, const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
-  const bool k3 = p.KH == 3 && p.KW == 3;  // the 3x3 filter has its MMA sequence unrolled
-  if (bn == 64) return k3 ? launch_row_conv<64, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<64, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
-  if (bn == 128) return k3 ? launch_row_conv<128, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<128, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
-  return k3 ? launch_row_conv<256, BMODE, 3>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<256, BMODE, 0>(mapA, mapB, p, smem_bytes, st);
+int launch_row_conv_bn(int bn, int mt, const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
+  // the 3x3 filter has its MMA sequence unrolled (weights resident, or streamed one filter row per stage)
+  const bool k3 = p.KH == 3 && p.KW == 3 && (p.resident || p.tps == 3);
+  if (mt == 2) {  // streamed weights only, BN <= 128
+    if (bn == 64) return k3 ? launch_row_conv<64, BMODE, 3, 2>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<64, BMODE, 0, 2>(mapA, mapB, p, smem_bytes, st);
+    return k3 ? launch_row_conv<128, BMODE, 3, 2>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<128, BMODE, 0, 2>(mapA, mapB, p, smem_bytes, st);
+  }
+  if (bn == 64) return k3 ? launch_row_conv<64, BMODE, 3, 1>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<64, BMODE, 0, 1>(mapA, mapB, p, smem_bytes, st);
+  if (bn == 128) return k3 ? launch_row_conv<128, BMODE, 3, 1>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<128, BMODE, 0, 1>(mapA, mapB, p, smem_bytes, st);
+  return k3 ? launch_row_conv<256, BMODE, 3, 1>(mapA, mapB, p, smem_bytes, st) : launch_row_conv<256, BMODE, 0, 1>(mapA, mapB, p, smem_bytes, st);
 }
 
 // Shared by forward (x, K-major weights) and the stride-1 data gradient (dY, weights in place).
@@ -426,7 +492,7 @@ int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, i
   p.a_stage_bytes = plan.a_stage_bytes; p.b_stages = plan.b_stages; p.tps = plan.tps; p.resident = plan.resident;
   p.out = out; p.ldo = nout; p.bias = bias; p.addend = addend; p.relu = relu;
   if (b_tap_x) for (int j = 0; j < kh * kw; ++j) p.b_tap_x[j] = b_tap_x[j];
-  return launch_row_conv_bn<BMODE>(bn, mapA, mapB, p, plan.smem_bytes, st);
+  return launch_row_conv_bn<BMODE>(bn, plan.mt, mapA, mapB, p, plan.smem_bytes, st);
 }
 
 }  // namespace

@@ -444,7 +444,7 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
   CUtensorMap mapA, mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
   if (rc) return rc;
-  const RowConvPlan plan = row_conv_plan(h, w, kh, kw, sh, sw, ph, pw, cin, cout, bn);
+  const RowConvPlan plan = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, cin, cout, bn);
   if (plan.ok) return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, nullptr, relu, y, (cudaStream_t)stream);
   rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
   if (rc) return rc;
@@ -486,7 +486,7 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   CUtensorMap mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32, true);
   if (rc) return rc;
-  const RowConvPlan plan = row_conv_plan(h, w, kh, kw, sh, sw, ph, pw, cout, cin, bn);
+  const RowConvPlan plan = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, cout, cin, bn);
   if (plan.ok) {
     // stride 1: dX = dY convolved with the filter rotated by 180 degrees, same padding
     int tap_x[64];

@@ -86,6 +86,21 @@ def test_conv_oracle(g, cfg):
     _conv_check(g, x, wt, b, dy, s, p)
 
 
+@pytest.mark.parametrize("cfg", [(8, 128, 16, 16, 128, 3, 1, 1, True), (3, 96, 20, 36, 72, 5, 1, 2, False), (4, 64, 56, 56, 64, 3, 1, 1, False)])
+def test_conv_two_tiles_per_weight_stage(g, cfg, monkeypatch):
+    """Large batches of layers with streamed weights compute two position tiles per weight stage; the
+    batch threshold is lowered here so that small problems take that path too (odd tile counts, tiles
+    straddling images, partial output-channel tiles)."""
+    monkeypatch.setenv("MTB_ROWCONV_MIN_ITEMS", "1")
+    n, ci, h, w, co, k, s, p, bias = cfg
+    rng = np.random.default_rng(77)
+    x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((co, ci, k, k)) / np.sqrt(ci * k * k)).astype(np.float32)
+    b = rng.standard_normal(co).astype(np.float32) if bias else None
+    dy = rng.standard_normal((n, co, h, w)).astype(np.float32)
+    _conv_check(g, x, wt, b, dy, s, p)
+
+
 @pytest.mark.parametrize("cfg", [(8, 64, 32, 32, 64, 3, 1, 1), (8, 64, 32, 32, 128, 3, 2, 1), (2, 20, 9, 11, 24, 3, 1, 1), (8, 3, 32, 32, 64, 3, 1, 1)])
 def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
     """dx returned with ``accumulate_dx`` equals dgrad + that tensor bit for bit, on the row-staged
