@@ -754,33 +754,42 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
   }
 }
 
-// dw[co][r] = sum_s partial[s][r][co]: 32x32 tiles, coalesced reads along co, smem transpose,
-// coalesced writes along r; splits added in index order.
+// dw[co][r] = sum_s partial[s][r][co]: a CTA takes 32 rows x 128 output channels, reads float4
+// along co (splits added in index order), transposes through shared memory and writes 128-byte
+// runs along r.
 __global__ void __launch_bounds__(1024) wgrad_reduce_transpose_kernel(const float* __restrict__ partial, float* __restrict__ dw, int Kw, int Cout,
                                                                        int splits) {
-  __shared__ float tile[32][33];
-  const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 32;
+  __shared__ float tile[128][33];
+  const int r0 = blockIdx.x * 32, c0 = blockIdx.y * 128;
   const long long plane = (long long)Kw * Cout;
   {
-    const int r = r0 + threadIdx.y, c = c0 + threadIdx.x;
-    float s0 = 0.f, s1 = 0.f, s2 = 0.f, s3 = 0.f;
-    if (r < Kw && c < Cout) {
+    const int r = r0 + threadIdx.y, c = c0 + 4 * threadIdx.x;
+    float4 s0 = make_float4(0.f, 0.f, 0.f, 0.f), s1 = s0;
+    if (r < Kw && c < Cout) {  // Cout % 4 == 0 on this path, so the four channels are in range together
       const float* q = partial + (long long)r * Cout + c;
       int z = 0;
-      for (; z + 3 < splits; z += 4) {  // four independent loads in flight; the grouping is fixed
-        s0 += q[z * plane];
-        s1 += q[(z + 1) * plane];
-        s2 += q[(z + 2) * plane];
-        s3 += q[(z + 3) * plane];
+      for (; z + 1 < splits; z += 2) {  // two independent loads in flight; the grouping is fixed
+        const float4 a = *reinterpret_cast<const float4*>(q + z * plane);
+        const float4 b = *reinterpret_cast<const float4*>(q + (z + 1) * plane);
+        s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+        s1.x += b.x; s1.y += b.y; s1.z += b.z; s1.w += b.w;
       }
-      for (; z < splits; ++z) s0 += q[z * plane];
+      if (z < splits) {
+        const float4 a = *reinterpret_cast<const float4*>(q + z * plane);
+        s0.x += a.x; s0.y += a.y; s0.z += a.z; s0.w += a.w;
+      }
     }
-    tile[threadIdx.y][threadIdx.x] = (s0 + s1) + (s2 + s3);
+    tile[4 * threadIdx.x + 0][threadIdx.y] = s0.x + s1.x;
+    tile[4 * threadIdx.x + 1][threadIdx.y] = s0.y + s1.y;
+    tile[4 * threadIdx.x + 2][threadIdx.y] = s0.z + s1.z;
+    tile[4 * threadIdx.x + 3][threadIdx.y] = s0.w + s1.w;
   }
   __syncthreads();
-  {
-    const int c = c0 + threadIdx.y, r = r0 + threadIdx.x;
-    if (r < Kw && c < Cout) dw[(long long)c * Kw + r] = tile[threadIdx.x][threadIdx.y];
+  const int r = r0 + threadIdx.x;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int cc = threadIdx.y + 32 * k, c = c0 + cc;
+    if (r < Kw && c < Cout) dw[(long long)c * Kw + r] = tile[cc][threadIdx.x];
   }
 }
 
@@ -874,7 +883,7 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   else MTB_LAUNCH_WGRAD(256, 64);
 #undef MTB_LAUNCH_WGRAD
   MTB_LAUNCH_CHECK("tc_wgrad_kernel");
-  dim3 rgrid((unsigned)((q.Kw + 31) / 32), (unsigned)((cout + 31) / 32));
+  dim3 rgrid((unsigned)((q.Kw + 31) / 32), (unsigned)((cout + 127) / 128));
   wgrad_reduce_transpose_kernel<<<rgrid, dim3(32, 32), 0, st>>>((const float*)workspace, dw, (int)q.Kw, cout, q.splits);
   MTB_LAUNCH_CHECK("wgrad_reduce_transpose_kernel");
   return MTB_OK;
