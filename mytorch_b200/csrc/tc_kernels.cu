@@ -120,12 +120,17 @@ struct GemmParams {
   int o_strided, o_Hc, o_Wc, o_H, o_W, o_h0, o_w0, o_sh, o_sw;
 };
 
+// A stage holds kKB reduction blocks of 32 (each one 128-byte swizzle span per operand row).  One
+// producer/consumer hand-over costs the issuing thread 300-400 cycles that do not overlap with MMA
+// work, and four MMAs of a narrow tile are only 192-256 cycles of work, so tiles up to 128 wide
+// take two blocks (8 MMAs) per stage.
 template <int BN>
 struct Cfg {
-  static constexpr int kStages = BN == 256 ? 4 : 6;
-  static constexpr uint32_t kABytes = 128 * 32 * 4;
-  static constexpr uint32_t kBBytes = BN * 32 * 4;
-  static constexpr uint32_t kStageBytes = kABytes + kBBytes;
+  static constexpr int kKB = BN <= 128 ? 2 : 1;
+  static constexpr int kStages = BN == 256 ? 4 : (BN == 128 ? 3 : 4);
+  static constexpr uint32_t kABytes = 128 * 32 * 4;   // one reduction block of A
+  static constexpr uint32_t kBBytes = BN * 32 * 4;    // one reduction block of B
+  static constexpr uint32_t kStageBytes = kKB * (kABytes + kBBytes);  // [A blocks][B blocks]
   static constexpr uint32_t kSmemBytes = kStages * kStageBytes + 1024;  // + alignment slack
   static constexpr uint32_t kTmemCols = 2 * BN;
 };
@@ -185,34 +190,39 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           pix_n = t / p.OH;
         }
         // reduction blocks in (tap, channel-block) order; plain GEMMs have a single "tap"
-        int kb = 0;
-        for (int kh = 0; kh < p.KH && ok; ++kh) {
-          for (int kw = 0; kw < p.KW && ok; ++kw) {
+        int kh = 0, kw = 0, cc = 0;
+        for (int kb = 0; kb < p.num_kb && ok; kb += C::kKB) {
+          const int nblk = p.num_kb - kb < C::kKB ? p.num_kb - kb : C::kKB;  // the last stage may hold one block
+          if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 1)) { ok = false; break; }
+          const uint32_t full = smem_u32(&bar_full[stage]);
+          mbar_expect_tx(full, (uint32_t)nblk * (C::kABytes + C::kBBytes));
+          const uint32_t st_base = smem_base + stage * C::kStageBytes;
+          for (int h = 0; h < nblk; ++h) {
+            const int kbh = kb + h;
             const int tap = kh * p.KW + kw;
-            for (int cc = 0; cc < p.cchunks; ++cc, ++kb) {
-              if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 1)) { ok = false; break; }
-              const uint32_t full = smem_u32(&bar_full[stage]);
-              mbar_expect_tx(full, C::kStageBytes);
-              const uint32_t a_dst = smem_base + stage * C::kStageBytes, b_dst = a_dst + C::kABytes;
-              if (AMODE == A_KMAJOR) {
-                tma_load_2d(a_dst, &mapA, full, kb * 32, m0);
-              } else if (AMODE == A_MNMAJOR) {
+            const uint32_t a_dst = st_base + h * C::kABytes, b_dst = st_base + C::kKB * C::kABytes + h * C::kBBytes;
+            if (AMODE == A_KMAJOR) {
+              tma_load_2d(a_dst, &mapA, full, kbh * 32, m0);
+            } else if (AMODE == A_MNMAJOR) {
 #pragma unroll
-                for (int j = 0; j < 4; ++j) tma_load_2d(a_dst + j * 4096, &mapA, full, m0 + 32 * j, kb * 32);
-              } else {
-                tma_load_im2col_4d(a_dst, &mapA, full, cc * 32, pix_w, pix_h, pix_n, (uint16_t)kw, (uint16_t)kh);
-              }
-              if (BMODE == B_KMAJOR) {
-                tma_load_2d(b_dst, &mapB, full, kb * 32, n0);
-              } else {
-                int bx = n0, by = kb * 32;
-                if (p.b_per_tap) { bx = p.b_tap_x[tap] + n0; by = cc * 32; }
+              for (int j = 0; j < 4; ++j) tma_load_2d(a_dst + j * 4096, &mapA, full, m0 + 32 * j, kbh * 32);
+            } else {
+              tma_load_im2col_4d(a_dst, &mapA, full, cc * 32, pix_w, pix_h, pix_n, (uint16_t)kw, (uint16_t)kh);
+            }
+            if (BMODE == B_KMAJOR) {
+              tma_load_2d(b_dst, &mapB, full, kbh * 32, n0);
+            } else {
+              int bx = n0, by = kbh * 32;
+              if (p.b_per_tap) { bx = p.b_tap_x[tap] + n0; by = cc * 32; }
 #pragma unroll
-                for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, full, bx + 32 * j, by);
-              }
-              if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+              for (int j = 0; j < BN / 32; ++j) tma_load_2d(b_dst + j * 4096, &mapB, full, bx + 32 * j, by);
+            }
+            if (++cc == p.cchunks) {
+              cc = 0;
+              if (++kw == p.KW) { kw = 0; ++kh; }
             }
           }
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
         }
       }
     }
@@ -227,7 +237,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     constexpr uint32_t a_step = AMODE == A_MNMAJOR ? (1024u >> 4) : (32u >> 4);  // per 8 of K, in 16-byte units
     constexpr uint32_t b_step = BMODE == B_MNMAJOR ? (1024u >> 4) : (32u >> 4);
     const uint32_t a_lo0 = AMODE == A_MNMAJOR ? desc_lo_mnmajor(smem_base) : desc_lo_kmajor(smem_base);
-    const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(smem_base + C::kABytes) : desc_lo_kmajor(smem_base + C::kABytes);
+    const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(smem_base + C::kKB * C::kABytes) : desc_lo_kmajor(smem_base + C::kKB * C::kABytes);
     int stage = 0;
     uint32_t phase = 0;
     int t = 0;
@@ -240,16 +250,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
       uint32_t acc = 0;
-      for (int kb = 0; kb < p.num_kb; ++kb) {
+      for (int kb = 0; kb < p.num_kb; kb += C::kKB) {
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 3));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
+        const bool second = C::kKB == 2 && kb + 1 < p.num_kb;
         if (elect_one()) {
           mma_tf32_words(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, acc);
           mma_tf32_words(d_tmem, a_lo + a_step, a_hi, b_lo + b_step, b_hi, idesc, 1u);
           mma_tf32_words(d_tmem, a_lo + 2 * a_step, a_hi, b_lo + 2 * b_step, b_hi, idesc, 1u);
           mma_tf32_words(d_tmem, a_lo + 3 * a_step, a_hi, b_lo + 3 * b_step, b_hi, idesc, 1u);
+          if (second) {
+            constexpr uint32_t a2 = C::kABytes >> 4, b2 = C::kBBytes >> 4;
+            mma_tf32_words(d_tmem, a_lo + a2, a_hi, b_lo + b2, b_hi, idesc, 1u);
+            mma_tf32_words(d_tmem, a_lo + a2 + a_step, a_hi, b_lo + b2 + b_step, b_hi, idesc, 1u);
+            mma_tf32_words(d_tmem, a_lo + a2 + 2 * a_step, a_hi, b_lo + b2 + 2 * b_step, b_hi, idesc, 1u);
+            mma_tf32_words(d_tmem, a_lo + a2 + 3 * a_step, a_hi, b_lo + b2 + 3 * b_step, b_hi, idesc, 1u);
+          }
           mma_commit(smem_u32(&bar_empty[stage]));
         }
         __syncwarp();
