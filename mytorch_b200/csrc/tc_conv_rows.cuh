@@ -129,10 +129,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           }
       }
       for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-        const long long q0 = (long long)(tile / p.n_tiles) * (128 * MT);
+        const int q0 = (tile / p.n_tiles) * (128 * MT);  // positions fit 31 bits (checked on the host)
         const int n0 = (tile % p.n_tiles) * BN;
-        const int v_lo = (int)(q0 / p.Wp) - p.PH;
-        const int nr = (int)((q0 + 128 * MT - 1) / p.Wp) + p.PH - v_lo + 1;
+        const int v_lo = q0 / p.Wp - p.PH;
+        const int nr = (q0 + 128 * MT - 1) / p.Wp + p.PH - v_lo + 1;
         // first image row: floor division (v_lo is -PH for the very first tile)
         const int img = v_lo >= 0 ? v_lo / p.Hv : -1;
         const int hrow = v_lo - img * p.Hv;
@@ -185,8 +185,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     bool ok = true;
     if (p.resident && blockIdx.x < tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bres), 0, abort_ptr, 17));
     for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
-      const long long q0 = (long long)(tile / p.n_tiles) * (128 * MT);
-      const int col = (int)(q0 % p.Wp);
+      const int col = ((tile / p.n_tiles) * (128 * MT)) % p.Wp;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 13));
@@ -298,7 +297,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const bool vec_ok = (p.ldo % 4 == 0) &&
                         (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.addend)) & 15u) == 0);
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
-      const long long q_item = (long long)(tile / p.n_tiles) * (128 * MT) + quarter * 32 + lane;
+      const int q_item = (tile / p.n_tiles) * (128 * MT) + quarter * 32 + lane;
       const int n0 = (tile % p.n_tiles) * BN;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
@@ -307,13 +306,13 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       bool valid[MT];
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
-        const long long q = q_item + 128 * m;
-        const long long v = q / p.Wp;
-        const int wp = (int)(q - v * p.Wp);
-        const long long img = v / p.Hv;
-        const int hrow = (int)(v - img * p.Hv);
+        const int q = q_item + 128 * m;
+        const int v = q / p.Wp;
+        const int wp = q - v * p.Wp;
+        const int img = v / p.Hv;
+        const int hrow = v - img * p.Hv;
         valid[m] = q < p.Q && hrow < p.H && wp >= p.PW && wp < p.W + p.PW;
-        ooff[m] = ((img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
+        ooff[m] = (((long long)img * p.H + hrow) * p.W + (wp - p.PW)) * p.ldo;
       }
       // With one tile per item the addend row is fetched while the MMAs of this tile still run:
       // loading it after the accumulator is ready would put a memory round trip per 32 columns
@@ -435,6 +434,7 @@ RowConvPlan row_conv_plan(int n, int h, int w, int kh, int kw, int sh, int sw, i
   r.Hv = h + ph;
   if (r.Wp > 256) return r;
   if ((double)w * h < 0.8 * (double)r.Wp * r.Hv) return r;  // too much padding: the im2col kernel wastes nothing
+  if ((long long)n * r.Hv * r.Wp > 0x7ffff000LL) return r;   // the kernel indexes positions with 32-bit integers
   const int taps = kh * kw;
   if (!row_conv_layout(r, 1, ph, pw, taps, kc, nout, bn, true)) return r;
   r.ok = true;
