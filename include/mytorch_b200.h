@@ -50,6 +50,10 @@ int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, i
  * (mytorch/autograd.py:160-170). */
 int mtb_conv2d_dgrad_add_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                              const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream);
+/* Introspection, host code only (works without a GPU): which kernel family forward / dgrad / wgrad
+ * would take for this shape and how the row-staged kernels lay out shared and tensor memory.
+ * out: 25 ints, see the definition in csrc/tc_kernels.cu.  No counterpart in the reference. */
+int mtb_conv2d_plan_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, int* out);
 /* dw[Cout,KH,KW,Cin]; split-K partials go to workspace and are summed in a fixed order */
 int mtb_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                          const float* dy, float* dw, void* workspace, long long workspace_bytes, void* stream);

@@ -58,6 +58,7 @@ _SIGNATURES = {
     "mtb_sgd_multi_f32": ([_I, _P, _P, _P, _P, _P, _D, _D, _D, _D, _I, _I, _D, _P], _I),
     "mtb_pack_scale_f32": ([_I, _P, _P, _P, _P, _D, _P], _I),
     "mtb_conv2d_workspace_bytes": (_CONV, _L),
+    "mtb_conv2d_plan_f32": (_CONV + [_P], _I),
     "mtb_conv2d_forward_f32": (_CONV + [_P, _P, _P, _P, _I, _P], _I),
     "mtb_conv2d_dgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_add_f32": (_CONV + [_P, _P, _P, _P, _P, _L, _P], _I),

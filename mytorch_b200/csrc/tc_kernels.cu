@@ -841,6 +841,59 @@ WgradPlan wgrad_plan(int n, int cin, int h, int w, int kh, int kw, int sh, int s
 
 }  // namespace
 
+// Which kernel family each of forward / data gradient / weight gradient would take for a shape
+// (pointers assumed 16-byte aligned), and, for the row-staged kernels, how their shared and tensor
+// memory is laid out against the furthest byte their copies write and their descriptors read.
+// Host code only: callable without a device (the SM count then defaults to 148).
+//   out[0..2]   path of forward, dgrad, wgrad: 0 CUDA-core, 1 im2col tcgen05, 2 row-staged tcgen05
+//   out[3..9]   forward, row-staged: dynamic smem bytes, activation stage bytes, last byte written by
+//               the row copies, last byte read through a descriptor, TMEM columns, tiles per item,
+//               1 if the filter is resident
+//   out[10..16] the same for dgrad
+//   out[17..24] wgrad, row-staged: dynamic smem bytes, X panel bytes, last byte written, last byte
+//               read, dY panel bytes, last byte written, last byte read, TMEM columns
+MTB_API int mtb_conv2d_plan_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, int* out) {
+  MTB_REQUIRE(out && n > 0 && cin > 0 && cout > 0 && h > 0 && w > 0 && kh > 0 && kw > 0 && sh > 0 && sw > 0, "conv2d_plan: bad arguments");
+  for (int i = 0; i < 25; ++i) out[i] = 0;
+  const float* al = reinterpret_cast<const float*>(uintptr_t(256));
+  const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
+  if (oh <= 0 || ow <= 0) return MTB_OK;
+  auto describe = [&](int slot, int kc, int nout, long long rows) {
+    const int bn = pick_bn_for(nout, rows);
+    const RowConvPlan q = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, kc, nout, bn);
+    if (!q.ok) return false;
+    const long long span = 128LL * q.mt;
+    out[slot + 0] = (int)q.smem_bytes;
+    out[slot + 1] = (int)q.a_stage_bytes;
+    out[slot + 2] = (int)(kRowLead + (long long)q.nr_max * q.Wp * 128);
+    out[slot + 3] = (int)(kRowLead + ((q.Wp - 1) + (span - 1) + (long long)(kh - 1) * q.Wp + (kw - 1) - pw + 1) * 128);
+    out[slot + 4] = 2 * q.mt * bn;
+    out[slot + 5] = q.mt;
+    out[slot + 6] = q.resident;
+    return true;
+  };
+  if (mtb_tc_conv2d_forward_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, al, al, al))
+    out[0] = describe(3, cin, cout, (long long)n * oh * ow) ? 2 : 1;
+  if (mtb_tc_conv2d_dgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, al, al, al))
+    out[1] = describe(10, cout, cin, (long long)n * h * w / (sh * sw)) ? 2 : 1;
+  if (mtb_tc_conv2d_wgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, al, al, al)) {
+    const WgradRowsPlan q = wgrad_rows_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
+    out[2] = q.ok ? 2 : 1;
+    if (q.ok) {
+      const int nr_y = (q.Wp - 1 + kWgRowsPB - 1) / q.Wp + 1, nr_x = nr_y + 2 * ph;
+      out[17] = (int)q.smem_bytes;
+      out[18] = (int)q.x_panel_bytes;
+      out[19] = (int)(kRowLead + (long long)nr_x * q.Wp * 128);
+      out[20] = (int)(kRowLead + ((q.Wp - 1) - pw + (long long)(kh - 1) * q.Wp + 4 * q.n_kwg - 1 + (kWgRowsPB - 1) + 1) * 128);
+      out[21] = (int)q.y_panel_bytes;
+      out[22] = (int)((long long)nr_y * q.Wp * 128);
+      out[23] = (int)(((q.Wp - 1) + (kWgRowsPB - 1) + 1) * 128);
+      out[24] = kh * q.n_kwg * q.ncc_g * q.bn;
+    }
+  }
+  return MTB_OK;
+}
+
 long long mtb_tc_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout) {
   if (cin % 32) return 0;
   WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);

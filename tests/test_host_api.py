@@ -179,6 +179,57 @@ def test_library_exports_every_declared_symbol():
     assert dll.mtb_version() >= 1
 
 
+def test_row_staged_kernels_never_plan_to_leave_their_memory():
+    """For every shape the row-staged tcgen05 kernels accept, the furthest byte their copies write and
+    their shifted descriptors read lies inside the stage or panel it belongs to, the stages fit the
+    227 KB of shared memory of a CTA and the accumulators fit the 512 columns of tensor memory.
+    (Host-side planning code only: runs without a GPU.)"""
+    from mytorch_b200.backends.cuda.env import LIBRARY_PATH
+
+    lib = ctypes.CDLL(LIBRARY_PATH)
+    lib.mtb_conv2d_plan_f32.argtypes = [ctypes.c_int] * 11 + [ctypes.POINTER(ctypes.c_int)]
+    out = (ctypes.c_int * 25)()
+    limit = 227 * 1024
+    seen = {0: 0, 1: 0, 2: 0}
+    sizes = [1, 2, 3, 4, 5, 7, 8, 9, 12, 14, 16, 17, 23, 28, 31, 32, 33, 40, 56, 57, 64, 100, 112, 127, 224, 250, 254, 255, 300]
+    for k in (3, 5, 7, 9):
+        p_ = k // 2
+        for h in sizes:
+            for w in sizes:
+                for cin in (32, 64, 96, 160, 256, 512):
+                    for cout in (4, 32, 64, 72, 128, 192, 256, 512):
+                        for n in (1, 7, 512):
+                            assert lib.mtb_conv2d_plan_f32(n, cin, h, w, k, k, 1, 1, p_, p_, cout, out) == 0
+                            fwd, dgrad, wgrad = out[0], out[1], out[2]
+                            seen[fwd] += 1
+                            for path, o in ((fwd, 3), (dgrad, 10)):
+                                if path == 2:
+                                    smem, stage, written, read, tmem, mt, resident = (out[o + i] for i in range(7))
+                                    assert 0 < smem <= limit and written <= stage and read <= stage, (n, cin, h, w, k, cout, list(out))
+                                    assert tmem <= 512 and mt in (1, 2) and resident in (0, 1)
+                            if wgrad == 2:
+                                smem, xp, xw, xr, yp, yw, yr, tmem = (out[17 + i] for i in range(8))
+                                assert 0 < smem <= limit and xw <= xp and xr <= xp and yw <= yp and yr <= yp, (n, cin, h, w, k, cout, list(out))
+                                assert 0 < tmem <= 512
+    for kh, kw in ((1, 3), (3, 1), (5, 3), (3, 7), (1, 9), (15, 3)):   # non-square filters
+        for h in (8, 17, 32, 56):
+            for w in (8, 17, 32, 56, 250):
+                for cin, cout in ((32, 16), (64, 64), (128, 256)):
+                    assert lib.mtb_conv2d_plan_f32(64, cin, h, w, kh, kw, 1, 1, kh // 2, kw // 2, cout, out) == 0
+                    for path, o in ((out[0], 3), (out[1], 10)):
+                        if path == 2:
+                            assert 0 < out[o] <= limit and out[o + 2] <= out[o + 1] and out[o + 3] <= out[o + 1] and out[o + 4] <= 512, (kh, kw, h, w, list(out))
+                    if out[2] == 2:
+                        assert 0 < out[17] <= limit and out[19] <= out[18] and out[20] <= out[18] and out[22] <= out[21] and out[23] <= out[21] and out[24] <= 512
+    assert seen[2] > 1000 and seen[1] > 1000   # the sweep reaches both tensor-core families
+    # shapes of the ResNet-18 step: row-staged at 32x32 and 16x16, im2col-mode at 8x8 and 4x4, CUDA cores for tiny inputs
+    for cfg, want in (((512, 64, 32, 32, 3, 3, 1, 1, 1, 1, 64), [2, 2, 2]), ((512, 128, 16, 16, 3, 3, 1, 1, 1, 1, 128), [2, 2, 2]),
+                      ((512, 256, 8, 8, 3, 3, 1, 1, 1, 1, 256), [1, 1, 1]), ((512, 64, 32, 32, 3, 3, 2, 2, 1, 1, 128), [1, 1, 1]),
+                      ((2, 20, 9, 11, 3, 3, 1, 1, 1, 1, 24), [0, 0, 0])):
+        lib.mtb_conv2d_plan_f32(*cfg, out)
+        assert list(out[0:3]) == want, (cfg, list(out))
+
+
 def test_shard_bounds_cover_batch():
     from mytorch_b200.parallel import shard_bounds
 
