@@ -10,8 +10,9 @@ Under torchrun (N > 1) every rank runs this file; rank 0 prints ONE JSON line.  
 `e2e`    : the same step fed from pinned host memory each iteration (H2D of images + labels,
            D2H of the loss) through the package's public API.
 `roofline`: the dominant kernel timed alone with CUDA events on its launch stream.
-`cpu_baseline` / `--impl reference`: the NumPy oracle (a restatement of the reference's CPU
-backend) timed on the host cores on a bounded sample of the same workload.
+`cpu_baseline` / `--impl reference`: the same ResNet-18 step at batch 64 on the host cores, run by
+the reference's own CPU backend when a checkout of the reference is present on the machine
+(`baseline/_ref` or `$MYTORCH_REFERENCE`), otherwise by the NumPy restatement of that backend.
 """
 from __future__ import annotations
 
@@ -130,26 +131,125 @@ def blas_threads():
         return os.cpu_count() or 1
 
 
+def find_reference():
+    """A checkout of the reference (a directory holding its ``mytorch`` package), if one is present:
+    ``baseline/_ref`` beside this file, else ``$MYTORCH_REFERENCE``."""
+    for cand in (os.path.join(ROOT, "baseline", "_ref"), os.environ.get("MYTORCH_REFERENCE", "")):
+        if cand and os.path.isdir(os.path.join(cand, "mytorch")):
+            return cand
+    return None
+
+
+def reference_cpu_step(ref_root, sample_batch, steps, warmup):
+    """The reference's own CPU backend driven through its public API (nn / autograd / optim) on the
+    same ResNet-18 step.  Its package is called ``mytorch``; nothing of this repository is on that path."""
+    sys.path.insert(0, ref_root)
+    import mytorch.nn as rnn
+    import mytorch.nn.functional as RF
+    from mytorch.optim import SGD as RSGD
+    from mytorch.rand_generator import manual_seed as rseed
+    from mytorch.tensor import Tensor as RT
+
+    class Block(rnn.Module):
+        def __init__(self, cin, cout, stride):
+            super().__init__()
+            self.conv1, self.bn1 = rnn.Conv2d(cin, cout, 3, stride, 1, bias=False), rnn.BatchNorm2d(cout)
+            self.conv2, self.bn2 = rnn.Conv2d(cout, cout, 3, 1, 1, bias=False), rnn.BatchNorm2d(cout)
+            self.downsample = None
+            if stride != 1 or cin != cout:
+                self.downsample = rnn.Sequential(rnn.Conv2d(cin, cout, 1, stride, 0, bias=False), rnn.BatchNorm2d(cout))
+            self.relu = rnn.ReLU()
+
+        def forward(self, x):
+            y = self.bn2(self.conv2(self.relu(self.bn1(self.conv1(x)))))
+            return self.relu(y + (x if self.downsample is None else self.downsample(x)))
+
+    class Net(rnn.Module):
+        def __init__(self):
+            super().__init__()
+            self.conv1, self.bn1, self.relu = rnn.Conv2d(3, 64, 3, 1, 1, bias=False), rnn.BatchNorm2d(64), rnn.ReLU()
+            cin = 64
+            for si, wd in enumerate((64, 128, 256, 512)):
+                setattr(self, f"layer{si + 1}", rnn.Sequential(Block(cin, wd, 2 if si else 1), Block(wd, wd, 1)))
+                cin = wd
+            self.fc = rnn.Linear(512, 10)
+
+        def forward(self, x):
+            x = self.relu(self.bn1(self.conv1(x)))
+            x = self.layer4(self.layer3(self.layer2(self.layer1(x))))
+            return self.fc(x.mean(dim=(2, 3)))
+
+    rng = np.random.default_rng(SEED)
+    x = rng.standard_normal((sample_batch, 3, 32, 32)).astype(np.float32)
+    t = rng.integers(0, 10, sample_batch).astype(np.int64)
+    rseed(SEED)
+    net = Net()
+    opt = RSGD(net.parameters(), lr=0.1, momentum=0.9)
+
+    def step():
+        loss = RF.cross_entropy(net(RT(cpu_array=x)), RT(cpu_array=t))
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+
+    for _ in range(warmup):
+        step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        step()
+    dt = (time.perf_counter() - t0) / steps
+    return sample_batch / dt, dt
+
+
+CPU_SAMPLE_BATCH = 64
+
+
+def cpu_arm(steps, warmup):
+    """(images/s, seconds per step, cpu_baseline dict): the reference itself when a checkout is
+    present on this machine, otherwise the NumPy restatement of its CPU backend."""
+    ref = find_reference()
+    if ref is not None:
+        ips, dt = reference_cpu_step(ref, CPU_SAMPLE_BATCH, steps, warmup)
+        kind, what = "reference", f"the reference's own CPU backend (checkout at {os.path.relpath(ref, ROOT)})"
+    else:
+        ips, dt = cpu_reference_step(CPU_SAMPLE_BATCH, steps, warmup)
+        kind, what = "port", ("the NumPy restatement of the reference CPU backend (no checkout of the reference on this machine: "
+                              "looked in baseline/_ref and $MYTORCH_REFERENCE)")
+    return ips, dt, {"value": ips, "unit": "images/s", "cores": blas_threads(), "kind": kind,
+                     "sample": f"{steps} full ResNet-18 training step(s) (forward, backward, SGD momentum) at batch {CPU_SAMPLE_BATCH} "
+                               f"of the global batch of {GLOBAL_BATCH}, after {warmup} warm-up step(s), with {what}"}
+
+
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    sample = 16
-    ips, dt = cpu_reference_step(sample, max(1, min(args.steps, 3)), max(1, min(args.warmup, 1)))
+    steps, warmup = max(1, min(args.steps, 2)), max(0, min(args.warmup, 1))
+    ips, dt, cpu = cpu_arm(steps, warmup)
     line = {
         "impl": "reference", "metric": "train_images_per_sec", "value": ips, "unit": "images/s", "n_gpus": args.gpus,
-        "steps": max(1, min(args.steps, 3)), "warmup": max(1, min(args.warmup, 1)), "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": steps, "warmup": warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f64/f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "parallelism": "cpu"},
-        "cpu_baseline": {"value": ips, "unit": "images/s", "cores": blas_threads(), "kind": "port",
-                         "sample": f"one full training step of the same ResNet-18 at batch {sample} (NumPy restatement of the "
-                                   "reference CPU backend; the reference is Python and is not present on this box)"},
+        "config": {"workload": WORKLOAD, "global_batch": GLOBAL_BATCH, "parallelism": "cpu", "sample_batch": CPU_SAMPLE_BATCH},
+        "cpu_baseline": cpu,
         "e2e": {"value": ips, "unit": "images/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
 # --------------------------------------------------------------------------- GPU arm
+
+def reference_first_loss(world):
+    """First-step loss of this very configuration (seed, batch, initial weights) computed by the
+    reference's CPU backend with the batch split into `world` shards (BatchNorm statistics per
+    shard, mean of the shard losses); recorded in a fixture because the reference cannot run here."""
+    path = os.path.join(ROOT, "tests", "golden", "data_parallel.npz")
+    if GLOBAL_BATCH != 512 or not os.path.exists(path):
+        return None
+    with np.load(path) as gd:
+        key = f"c3_b512/w{world}/loss"
+        return float(gd[key]) if key in gd else None
+
 
 def kernel_legs(torch, env, peaks):
     """Time the dominant kernels alone (CUDA events on the launch stream, buffers rotated so that
@@ -274,14 +374,6 @@ def run_gpu_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
-    trace_dir = os.environ.get("MTB_BENCH_TRACE")  # directory for per-rank progress logs (debugging aid)
-
-    def trace(msg):
-        if trace_dir:
-            with open(os.path.join(trace_dir, f"trace_rank{rank}.log"), "a") as f:
-                f.write(f"{time.time():.3f} {msg}\n")
-
-    trace("start")
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             sys.exit(f"--gpus {args.gpus} needs torchrun: python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...")
@@ -289,7 +381,6 @@ def run_gpu_arm(args):
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
-        trace("process group up")
 
     import mytorch_b200 as mt
     import mytorch_b200.nn.functional as F
@@ -333,13 +424,14 @@ def run_gpu_arm(args):
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
-
-    trace("model built")
     first_loss = step().item()
-    trace(f"first eager step done, loss {first_loss}")
+    if world > 1:  # the job's loss is the mean of the shard losses
+        fl = torch.tensor([first_loss], device=dev)
+        dist.all_reduce(fl)
+        first_loss = float(fl.item()) / world
+    loss_ref = reference_first_loss(world)
     step()
     torch.cuda.synchronize()
-    trace("second eager step done")
     runner = None
     if not args.no_graph:
         before = env.lib.launches
@@ -347,7 +439,6 @@ def run_gpu_arm(args):
         sg.capture()
         calls_per_step = env.lib.launches - before
         runner = sg
-        trace("graph captured")
     else:
         before = env.lib.launches
         step()
@@ -391,21 +482,24 @@ def run_gpu_arm(args):
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
-    trace("warm-up done")
-    total_ms = timed_region(lambda i: run_resident(), args.steps)
-    trace("timed region done")
-    clocks = sampler.stop() if rank == 0 else None
+    # the timed region of K steps is short (tens of milliseconds), so it is repeated and the median
+    # region is reported, with the spread beside it; the clock sampler runs across all repeats
+    resident_ms = [timed_region(lambda i: run_resident(), args.steps) for _ in range(args.repeats)]
     if runner is not None:
         runner.prefetch([host_x[0], host_t[0]])
     for i in range(2):
         run_e2e(i)
-    e2e_ms = timed_region(lambda i: run_e2e(i + 2), args.steps)
+    e2e_all = [timed_region(lambda i: run_e2e(i + 2), args.steps) for _ in range(args.repeats)]
+    clocks = sampler.stop() if rank == 0 else None
     last_loss = run_e2e(args.steps + 2)
-    trace("e2e done")
 
+    total_ms, e2e_ms = statistics.median(resident_ms), statistics.median(e2e_all)
     ms_per_step = total_ms / args.steps
     value = GLOBAL_BATCH / (ms_per_step * 1e-3)
     e2e_value = GLOBAL_BATCH / (e2e_ms / args.steps * 1e-3)
+    tc_status = env.tensor_core_status()
+    if tc_status != 0:
+        sys.exit(f"a bounded wait inside a tensor-core kernel ran out (status {tc_status}): results are not valid")
     step_flops = 3 * conv_flops_resnet18(GLOBAL_BATCH) - 2 * GLOBAL_BATCH * 32 * 32 * 64 * 27  # stem dgrad is not executed
 
     roof, kernels, cpu = None, None, None
@@ -426,9 +520,10 @@ def run_gpu_arm(args):
             kernels["cublas_tf32_8192_tflops"] = 2 * 8192 ** 3 / (best * 1e-3) / 1e12
         except Exception as e:  # measurement aid only
             kernels["cublas_tf32_8192_tflops"] = f"unavailable: {e}"
-        ips, dt = cpu_reference_step(16, 1, 1)
-        cpu = {"value": ips, "unit": "images/s", "cores": blas_threads(), "kind": "port",
-               "sample": "one full ResNet-18 training step at batch 16 with the NumPy restatement of the reference CPU backend"}
+        _, _, cpu = cpu_arm(1, 0)
+        tc_status = env.tensor_core_status()
+        if tc_status != 0:
+            sys.exit(f"a bounded wait inside a tensor-core kernel ran out in the single-kernel legs (status {tc_status})")
 
     if rank == 0:
         line = {
@@ -443,22 +538,23 @@ def run_gpu_arm(args):
                     "d2h_bytes_per_step": 4 * world},
             "gpu_launches": calls_per_step * args.steps,
             "gpu_launches_note": "C-ABI calls per step x steps; each call enqueues 1-3 kernels of libmytorch_b200.so",
-            "loss_first": first_loss, "loss_last": last_loss,
+            "loss_first": first_loss, "loss_first_ref": loss_ref, "loss_first_rel_err": None if loss_ref is None else abs(first_loss - loss_ref) / abs(loss_ref),
+            "loss_last": last_loss, "tensor_core_status": tc_status,
+            "repeats": {"n": args.repeats, "ms_per_step_min": min(resident_ms) / args.steps, "ms_per_step_max": max(resident_ms) / args.steps,
+                        "e2e_ms_per_step_min": min(e2e_all) / args.steps, "e2e_ms_per_step_max": max(e2e_all) / args.steps,
+                        "reported": "median of the repeated K-step regions"},
             "clocks": clocks, "roofline": roof, "kernels": kernels, "cpu_baseline": cpu,
         }
         print(json.dumps(line))
-    trace("printed")
     if world > 1:
         # Tearing down a NCCL process group whose collectives were captured in a CUDA graph that is
         # still alive blocks in this PyTorch/NCCL combination; finish with a barrier and leave the
         # process without running the communicator's destructor.
         dist.barrier()
         torch.cuda.synchronize()
-        trace("exit")
         sys.stdout.flush()
         sys.stderr.flush()
         os._exit(0)
-    trace("exit")
 
 
 def main():
@@ -468,6 +564,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--repeats", type=int, default=5, help="how many times the timed region of K steps is repeated (the median is reported)")
     ap.add_argument("--no-graph", action="store_true", help="launch every operator eagerly instead of replaying a CUDA graph")
     ap.add_argument("--global-batch", type=int, default=GLOBAL_BATCH,
                     help="profiling aid: run the step at another global batch (the benchmark configuration is 512)")

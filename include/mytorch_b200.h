@@ -33,6 +33,11 @@ int mtb_device_check(void); /* MTB_OK iff the current device is compute capabili
  * 0 = fine, otherwise a bounded in-kernel wait ran out and that kernel exited without finishing.
  * No counterpart in the reference (its kernels have no waits). status_out is a HOST pointer. */
 int mtb_tc_status(int* status_out);
+/* Self-test of that give-up path (no counterpart in the reference): one CTA allocates tensor memory and
+ * waits at most limit_cycles (1..2e8 SM cycles, i.e. at most ~0.1 s) on an mbarrier that nothing completes;
+ * the wait runs out, `code` (non-zero) lands in the status word, tensor memory is freed and the kernel
+ * returns.  Nothing traps; the context stays usable. */
+int mtb_tc_wait_selftest(long long limit_cycles, int code, void* stream);
 
 /* ---- convolution (replaces ConvForwardImplicitGEMM_float32 / ConvBackwardImplicitGEMM_float32,
  *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from
@@ -120,8 +125,10 @@ int mtb_colsum_f32(const float* a, long long rows, int c, float scale, float* ou
 /* The same column sum for callers that can neither pass nor allocate scratch (an embedder whose arena
  * owns all device memory, a step loop where driver allocations are off limits).  It has no counterpart
  * in the reference.  Partials live in a 1 MiB device array inside the library; c <= 1024, otherwise
- * MTB_ERR_UNSUPPORTED.  Performs no allocation.  The first call on each device resolves the array's
- * address and should happen before any stream capture.  Calls share the array: do not let two of
+ * MTB_ERR_UNSUPPORTED.  The call itself allocates nothing.  The first call on each device resolves the
+ * array's address; with lazy module loading the driver may load the library's device code and back
+ * the array at that moment, so make one warm-up call per device before the stretch of code in which
+ * nothing may allocate, and before any stream capture.  Calls share the array: do not let two of
  * them overlap on one GPU. */
 int mtb_colsum_noalloc_f32(const float* a, long long rows, int c, float scale, float* out, void* stream);
 int mtb_nhwc_spatial_sum_f32(const float* x, float* y, int n, int c, int hw, float scale, void* stream);

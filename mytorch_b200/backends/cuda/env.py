@@ -65,6 +65,7 @@ _SIGNATURES = {
     "mtb_conv2d_wgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_gemm_f32": ([_I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _P], _I),
     "mtb_tc_status": ([_P], _I),
+    "mtb_tc_wait_selftest": ([_L, _I, _P], _I),
 }
 
 LIBRARY_PATH = os.environ.get(
@@ -129,9 +130,13 @@ class CudaEnv:
         self.lib = NativeLibrary()
         self.lib.device_check()
         self._scratch = {}
+        self._retired_scratch = []
 
     def stream(self):
         return self.torch.cuda.current_stream().cuda_stream
+
+    def capturing(self):
+        return bool(self.torch.cuda.is_current_stream_capturing())
 
     def tensor_core_status(self):
         """Synchronises and returns the status word of the tensor-core kernels (0 = fine; non-zero
@@ -154,6 +159,10 @@ class CudaEnv:
         dev = self.torch.cuda.current_device()
         buf = self._scratch.get(dev)
         if buf is None or buf.numel() < nbytes:
+            if buf is not None:
+                # a captured graph may hold this block's address: it is kept for the life of the
+                # process so that the allocator can never hand it to a tensor a replay would overwrite
+                self._retired_scratch.append(buf)
             buf = self.alloc(max(int(nbytes), 1 << 20), dev)
             self._scratch[dev] = buf
         return buf.data_ptr(), buf.numel()

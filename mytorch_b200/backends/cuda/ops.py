@@ -297,7 +297,10 @@ def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, ru
     n, c, h, w = x.shape
     y, mean, var = _new(x.shape, x), _new((c,), x), _new((c,), x)
     ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
-    env.lib.batch_norm2d_forward_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), int(bool(training)), float(momentum),
+    # without running statistics the reference normalises with batch statistics in eval mode too
+    # (``mytorch/backends/cpu/ops/batch_norm.py:40-46``)
+    use_batch_stats = bool(training) or running_mean is None or running_var is None
+    env.lib.batch_norm2d_forward_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), int(use_batch_stats), float(momentum),
                                      _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), int(bool(relu)), ws, ws_bytes, env.stream())
     return y, mean, var
 
@@ -696,9 +699,17 @@ def cuda_cross_entropy_backward(output_grad, input, target):
 
 # ---------------------------------------------------------------------------- optimiser
 
+def _refuse_first_step_in_capture(env, is_first_time):
+    """A captured first step would bake "momentum buffer = gradient" into the graph and every replay
+    would reset the momentum; the momentum buffers must exist (one eager step) before capture."""
+    if is_first_time and env.capturing():
+        raise RuntimeError("optimizer state does not exist yet: run one eager optimizer step before capturing the step in a CUDA graph")
+
+
 @_reg("cuda", "sgd")
 def cuda_sgd(param, momentum_buffer, is_first_time, lr, weight_decay, momentum, dampening, nesterov, maximize):
     env = _env(param)
+    _refuse_first_step_in_capture(env, is_first_time)
     env.lib.sgd_f32(_ptr(param), _ptr(param.grad), _ptr(momentum_buffer), _numel(param.shape), int(bool(is_first_time)), float(lr),
                     float(weight_decay), float(momentum), float(dampening), int(bool(nesterov)), int(bool(maximize)), 1.0, env.stream())
 
@@ -709,6 +720,7 @@ def cuda_sgd_multi(entries, lr, weight_decay, momentum, dampening, nesterov, max
     if not entries:
         return
     env = _env(entries[0][0])
+    _refuse_first_step_in_capture(env, any(f for _, _, f in entries))
     k = len(entries)
     vp = ctypes.c_void_p
     params = (vp * k)(*[_ptr(p) for p, _, _ in entries])

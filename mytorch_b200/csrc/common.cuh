@@ -17,6 +17,9 @@ enum MtbStatus {
 
 int mtb_fail(int code, const char* fmt, ...);
 int mtb_sm_count();
+// Opt a kernel in to `bytes` of dynamic shared memory on the CURRENT device.  The attribute is kept
+// per device, so `done_mask` (one per kernel, zero-initialised) remembers the ordinals already set.
+int mtb_opt_in_smem(const void* kernel, int bytes, unsigned long long* done_mask);
 
 #define MTB_REQUIRE(cond, ...) \
   do { if (!(cond)) return mtb_fail(MTB_ERR_INVALID, __VA_ARGS__); } while (0)

@@ -181,30 +181,37 @@ namespace {
 
 constexpr int kNoAllocMaxChannels = 1024;
 constexpr int kNoAllocMaxPartials = 256;
+constexpr int kNoAllocMaxDevices = 64;
 // 256 partial rows x 1024 channels x 4 bytes = 1 MiB per GPU.
 static __device__ __align__(256) float g_colsum_scratch[kNoAllocMaxPartials * kNoAllocMaxChannels];
 
 // In host code the name of a __device__ array is only a host-side stand-in; the device address
 // has to be asked for, once per device, with that device current.
 float* noalloc_scratch_for_current_device(int* status) {
-  static float* cached[64] = {nullptr};
+  // one slot per device ordinal; host threads racing on a first call store the same address
+  static float* cached[kNoAllocMaxDevices] = {nullptr};
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= 64) {
+  if (e != cudaSuccess) {
     *status = mtb_fail(MTB_ERR_CUDA, "colsum_noalloc: cudaGetDevice failed: %s", cudaGetErrorString(e));
     return nullptr;
   }
-  if (!cached[dev]) {
-    float* ptr = nullptr;
+  if (dev < 0 || dev >= kNoAllocMaxDevices) {
+    *status = mtb_fail(MTB_ERR_UNSUPPORTED, "colsum_noalloc: device ordinal %d is outside the %d ordinals this entry point keeps an address for",
+                       dev, kNoAllocMaxDevices);
+    return nullptr;
+  }
+  float* ptr = __atomic_load_n(&cached[dev], __ATOMIC_ACQUIRE);
+  if (!ptr) {
     e = cudaGetSymbolAddress((void**)&ptr, g_colsum_scratch);
     if (e != cudaSuccess || !ptr) {
       *status = mtb_fail(MTB_ERR_CUDA, "colsum_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return nullptr;
     }
-    cached[dev] = ptr;
+    __atomic_store_n(&cached[dev], ptr, __ATOMIC_RELEASE);
   }
   *status = MTB_OK;
-  return cached[dev];
+  return ptr;
 }
 
 }  // namespace
@@ -213,8 +220,10 @@ float* noalloc_scratch_for_current_device(int* status) {
 // allocation of any kind: the per-CTA partial sums go to a 1 MiB array that is part of the
 // library.  Limits: c <= 1024 (more is rejected with MTB_ERR_UNSUPPORTED); at most 256 partial
 // rows are used, so very tall matrices run with fewer CTAs than mtb_colsum_f32 would use.
-// The first call on a device looks up the array's device address (cudaGetSymbolAddress); make
-// that first call before any stream capture begins.  All calls on a device share the one array
+// The first call on a device looks up the array's device address (cudaGetSymbolAddress), and with
+// lazy module loading that lookup is also the moment the driver loads this module and backs the
+// array: make one warm-up call per device before the region in which nothing may allocate and
+// before any stream capture begins.  All calls on a device share the one array
 // (it keeps the previous call's partials, every element that is read is rewritten first), so two
 // calls that may overlap on the GPU - different streams, no dependency - race with each other.
 MTB_API int mtb_colsum_noalloc_f32(const float* a, long long rows, int c, float scale, float* out, void* stream) {

@@ -25,6 +25,16 @@ int mtb_sm_count() {
   return cached[dev];
 }
 
+int mtb_opt_in_smem(const void* kernel, int bytes, unsigned long long* done_mask) {
+  int dev = 0;
+  MTB_CUDA(cudaGetDevice(&dev));
+  const bool tracked = dev >= 0 && dev < 64;
+  if (tracked && ((__atomic_load_n(done_mask, __ATOMIC_ACQUIRE) >> dev) & 1ull)) return MTB_OK;
+  MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  if (tracked) __atomic_fetch_or(done_mask, 1ull << dev, __ATOMIC_RELEASE);
+  return MTB_OK;
+}
+
 MTB_API const char* mtb_last_error() { return g_last_error; }
 
 MTB_API int mtb_version() { return 1; }

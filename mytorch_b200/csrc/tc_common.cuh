@@ -49,20 +49,23 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 
 // Returns false when the wait was abandoned (limit reached here, or another role aborted).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code, long long limit_cycles) {
   if (mbar_try_wait(bar, parity)) return true;
   long long start = clock64();
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - start > kWaitCycles) {
+      if (clock64() - start > limit_cycles) {
         *abort_flag = 1;
         atomicCAS(&g_tc_status[0], 0, code);
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  return mbar_wait_limit(bar, parity, abort_flag, code, kWaitCycles);
 }
 
 // ---- TMA loads (global -> shared, completion on an mbarrier) ----

@@ -451,11 +451,8 @@ RowConvPlan row_conv_plan(int n, int h, int w, int kh, int kw, int sh, int sw, i
 template <int BN, int BMODE, int FK, int MT>
 int launch_row_conv(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
   auto kernel = tc_conv_rows_kernel<BN, BMODE, FK, MT>;
-  static bool configured = false;
-  if (!configured) {
-    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
-    configured = true;
-  }
+  static unsigned long long configured = 0;
+  if (int rc = mtb_opt_in_smem((const void*)kernel, 227 * 1024 - 1024, &configured)) return rc;
   const int items = ((p.m_tiles + MT - 1) / MT) * p.n_tiles;
   const int grid = items < mtb_sm_count() ? items : mtb_sm_count();
   kernel<<<grid, 192, smem_bytes, st>>>(mapA, mapB, p);
@@ -791,11 +788,8 @@ WgradRowsPlan wgrad_rows_plan(int n, int cin, int h, int w, int kh, int kw, int 
 template <int BN, int FIX>
 int launch_wgrad_rows(const CUtensorMap& mapX, const CUtensorMap& mapDY, const WgradRowsParams& p, int grid, uint32_t smem_bytes, cudaStream_t st) {
   auto kernel = tc_wgrad_rows_kernel<BN, FIX>;
-  static bool configured = false;
-  if (!configured) {
-    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024 - 1024));
-    configured = true;
-  }
+  static unsigned long long configured = 0;
+  if (int rc = mtb_opt_in_smem((const void*)kernel, 227 * 1024 - 1024, &configured)) return rc;
   kernel<<<grid, 192, smem_bytes, st>>>(mapX, mapDY, p);
   MTB_LAUNCH_CHECK("tc_wgrad_rows_kernel");
   return MTB_OK;

@@ -353,11 +353,8 @@ template <int BN, int AMODE, int BMODE>
 int launch_tc(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t st) {
   using C = Cfg<BN>;
   auto kernel = tc_gemm_kernel<BN, AMODE, BMODE>;
-  static bool configured = false;
-  if (!configured) {
-    MTB_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)C::kSmemBytes));
-    configured = true;
-  }
+  static unsigned long long configured = 0;
+  if (int rc = mtb_opt_in_smem((const void*)kernel, (int)C::kSmemBytes, &configured)) return rc;
   int tiles = p.m_tiles * p.n_tiles;
   int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
   kernel<<<grid, 192, C::kSmemBytes, st>>>(mapA, mapB, p);
@@ -408,6 +405,45 @@ MTB_API int mtb_tc_status(int* status_out) {
     int z[8] = {0};
     MTB_CUDA(cudaMemcpyToSymbol(g_tc_status, z, sizeof(z)));
   }
+  return MTB_OK;
+}
+
+// Self-test of the give-up path every tensor-core kernel shares: a CTA allocates tensor memory,
+// then one thread waits (with the given limit) on an mbarrier that nothing will ever complete.
+// The wait runs out, the waiter records `code` in the status word and raises the CTA's abort flag,
+// and the kernel tears down like the real ones: tensor memory is freed, the CTA exits.
+namespace {
+__global__ void __launch_bounds__(64, 1) tc_wait_selftest_kernel(long long limit_cycles, int code) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t tmem_slot;
+  __shared__ int abort_flag;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&tmem_slot), 32);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  if (warp == 0 && lane == 0) mbar_wait_limit(smem_u32(&bar), 0, &abort_flag, code, limit_cycles);
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_slot, 32);
+  }
+}
+}  // namespace
+
+MTB_API int mtb_tc_wait_selftest(long long limit_cycles, int code, void* stream) {
+  MTB_REQUIRE(limit_cycles > 0 && limit_cycles <= 200000000LL && code != 0, "tc_wait_selftest: limit must be 1..2e8 cycles and code non-zero");
+  tc_wait_selftest_kernel<<<1, 64, 0, (cudaStream_t)stream>>>(limit_cycles, code);
+  MTB_LAUNCH_CHECK("tc_wait_selftest_kernel");
   return MTB_OK;
 }
 
@@ -941,12 +977,9 @@ int mtb_tc_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   const int grid = units < mtb_sm_count() ? units : mtb_sm_count();
 #define MTB_LAUNCH_WGRAD(BN_, PB_)                                                                                      \
   do {                                                                                                                  \
-    static bool configured = false;                                                                                     \
-    if (!configured) {                                                                                                  \
-      MTB_CUDA(cudaFuncSetAttribute(tc_wgrad_kernel<BN_, PB_>, cudaFuncAttributeMaxDynamicSharedMemorySize,            \
-                                    (int)WCfg<BN_, PB_>::kSmemBytes));                                                  \
-      configured = true;                                                                                                \
-    }                                                                                                                   \
+    static unsigned long long configured = 0;                                                                           \
+    if (int rc_ = mtb_opt_in_smem((const void*)tc_wgrad_kernel<BN_, PB_>, (int)WCfg<BN_, PB_>::kSmemBytes, &configured)) \
+      return rc_;                                                                                                       \
     tc_wgrad_kernel<BN_, PB_><<<grid, 192, WCfg<BN_, PB_>::kSmemBytes, st>>>(mapX, mapDY, p);                           \
   } while (0)
   if (q.bn == 64) MTB_LAUNCH_WGRAD(64, 64);

@@ -19,6 +19,20 @@ import numpy as np
 from numpy.lib.stride_tricks import sliding_window_view
 
 
+def round_tf32(a):
+    """float32 values rounded to TF32 (10 mantissa bits, round to nearest, ties to even), returned as
+    float32.  No counterpart in the reference, whose GPU kernels multiply in fp32: this models the one
+    place where the tensor-core kernels deviate from fp32 arithmetic.  Their operands pass through
+    tensor maps of type TFLOAT32, and the copy engine rounds them this way on the way into shared
+    memory (measured: results agree with this model to 1e-5, against 3e-4 for unrounded operands and
+    9e-4 for truncation); products and sums are then exact / fp32.  Feeding rounded operands to the
+    functions below therefore predicts the tensor-core results up to fp32 accumulation error."""
+    a = np.ascontiguousarray(a, dtype=np.float32)
+    u = a.view(np.uint32).astype(np.uint64)
+    u = (u + 0xFFF + ((u >> 13) & 1)) & 0xFFFFE000
+    return u.astype(np.uint32).view(np.float32).reshape(a.shape)
+
+
 def _pair(v):
     return (int(v), int(v)) if np.isscalar(v) else tuple(int(i) for i in v)
 

@@ -46,3 +46,14 @@ def summarize(arr, sample=64):
 @pytest.fixture(scope="session")
 def golden():
     return load_golden
+
+
+@pytest.fixture(autouse=True, scope="module")
+def tensor_core_kernels_never_gave_up():
+    """Every bounded wait inside the tensor-core kernels gives up after its limit and records a code
+    in a status word instead of hanging; a module of GPU tests must end with that word still clear."""
+    yield
+    from mytorch_b200.backends.cuda.env import CudaEnv
+
+    if CudaEnv._instance is not None:
+        assert CudaEnv._instance.tensor_core_status() == 0

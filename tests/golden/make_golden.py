@@ -300,10 +300,68 @@ def model_cases():
     np.savez_compressed(os.path.join(OUT, "models.npz"), **out)
 
 
+def _shard_bounds(n, rank, world):
+    base, extra = divmod(n, world)
+    lo = rank * base + min(rank, extra)
+    return lo, lo + base + (1 if rank < extra else 0)
+
+
+def sharded_step(build, seed, x, t, world, lr, momentum, out, tag, want_grads=True):
+    """Data parallelism emulated with the reference itself: every shard of the batch runs through
+    the same initial weights (BatchNorm therefore sees the statistics of its shard only), the
+    shard gradients are averaged, and one SGD step is taken with the average.  The reported loss
+    is the mean of the shard losses.  With world == 1 this is the plain reference step."""
+    losses, sums = [], None
+    for r in range(world):
+        lo, hi = _shard_bounds(x.shape[0], r, world)
+        manual_seed(seed)
+        model = build()
+        loss = F.cross_entropy(model(T(x[lo:hi])), T(t[lo:hi]))
+        losses.append(loss.item())
+        if not want_grads:
+            continue
+        loss.backward()
+        grads = [(k, np.asarray(npy(v.grad), dtype=np.float64)) for k, v in model.named_parameters()]
+        sums = grads if sums is None else [(k, a + b) for (k, a), (_, b) in zip(sums, grads)]
+    out[f"{tag}/shard_losses"] = np.array(losses)
+    out[f"{tag}/loss"] = np.array(float(np.mean(losses)))
+    if not want_grads:
+        return
+    avg = [(k, (a / world).astype(f32)) for k, a in sums]
+    summarize(f"{tag}/grad", avg, out)
+    manual_seed(seed)
+    model = build()
+    opt = SGD(model.parameters(), lr=lr, momentum=momentum)
+    for (k, p), (_, g) in zip(model.named_parameters(), avg):
+        p.grad = T(g)
+    opt.step()
+    summarize(f"{tag}/param", [(k, npy(v)) for k, v in model.named_parameters()], out)
+
+
+def dp_cases():
+    """Sharded data-parallel steps: a reduced-width ResNet-18 on 2 and 4 shards with gradients, and the
+    benchmark configuration (full-width ResNet-18, batch 512, seed 1003) with gradients on 1 shard
+    and first-step losses on 2, 4 and 8 shards."""
+    out = {}
+    rng = np.random.default_rng(2002)
+    x = rng.standard_normal((16, 3, 32, 32)).astype(f32)
+    t = rng.integers(0, 10, 16).astype(np.int64)
+    for world in (2, 4):
+        sharded_step(lambda: ResNet18((16, 32, 64, 64)), 2002, x, t, world, 0.1, 0.9, out, f"dp_small/w{world}")
+    rng = np.random.default_rng(1003)
+    x = rng.standard_normal((512, 3, 32, 32)).astype(f32)
+    t = rng.integers(0, 10, 512).astype(np.int64)
+    full = lambda: ResNet18((64, 128, 256, 512))
+    sharded_step(full, 1003, x, t, 1, 0.1, 0.9, out, "c3_b512/w1")
+    for world in (2, 4, 8):
+        sharded_step(full, 1003, x, t, world, 0.1, 0.9, out, f"c3_b512/w{world}", want_grads=False)
+    np.savez_compressed(os.path.join(OUT, "data_parallel.npz"), **out)
+
+
 if __name__ == "__main__":
-    conv_cases()
-    bn_cases()
-    pool_cases()
-    misc_cases()
-    model_cases()
+    only = sys.argv[2:]  # optional: names of the fixture groups to regenerate
+    groups = {"conv": conv_cases, "bn": bn_cases, "pool": pool_cases, "misc": misc_cases, "models": model_cases, "dp": dp_cases}
+    for name, fn in groups.items():
+        if not only or name in only:
+            fn()
     print("golden fixtures written to", OUT)

@@ -24,7 +24,9 @@ def test_noalloc_colsum_matches_workspace_variant_on_consecutive_calls():
     env = CudaEnv.instance()
     lib = env.lib
     rng = np.random.default_rng(2024)
-    for rows, c, scale in [(4096, 64, 1.0), (777, 24, 0.5), (50000, 512, 1.0), (33, 7, 2.0)]:
+    # the last two sit at the limit (1024 channels) and just under it (1023: not a multiple of 4, so the
+    # scalar kernel runs over several column blocks)
+    for rows, c, scale in [(4096, 64, 1.0), (777, 24, 0.5), (50000, 512, 1.0), (33, 7, 2.0), (3000, 1024, 1.0), (2100, 1023, 0.25)]:
         a = rng.standard_normal((rows, c)).astype(np.float32)
         at = g.dev(a)
         ref_out, new_out = g.dev(np.zeros(c, np.float32)), g.dev(np.full(c, 7.0, np.float32))
@@ -39,3 +41,26 @@ def test_noalloc_colsum_matches_workspace_variant_on_consecutive_calls():
         big = g.dev(np.zeros((8, 2048), np.float32))
         out = g.dev(np.zeros(2048, np.float32))
         lib.colsum_noalloc_f32(big._native_array.ptr, 8, 2048, 1.0, out._native_array.ptr, env.stream())
+
+
+def test_noalloc_colsum_leaves_free_device_memory_unchanged():
+    """After one warm-up call (which may make the driver load the library's device code), further
+    calls neither take nor return device memory: the free-memory figure the driver reports stays put."""
+    import gpu_util as g
+    from mytorch_b200.backends.cuda.env import CudaEnv
+
+    env = CudaEnv.instance()
+    torch = env.torch
+    rng = np.random.default_rng(7)
+    a = rng.standard_normal((20000, 256)).astype(np.float32)
+    at, out = g.dev(a), g.dev(np.zeros(256, np.float32))
+    call = lambda: env.lib.colsum_noalloc_f32(at._native_array.ptr, 20000, 256, 1.0, out._native_array.ptr, env.stream())
+    call()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(5):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before
+    assert rel_err(g.host(out), a.astype(np.float64).sum(axis=0)) < 1e-5
