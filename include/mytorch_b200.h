@@ -113,6 +113,9 @@ int mtb_add_bias_rows_f32(const float* x, const float* bias, float* y, long long
  * permute_reference, mytorch/native/cuda/basic_ops.cu/source.cu:5-41) */
 int mtb_binary_strided_f32(int op, int ndim, const long long* shape, const long long* x_strides, const long long* y_strides,
                            const long long* z_strides, const float* x, const float* y, float* z, float alpha, void* stream);
+/* dst[rows][c_dst] from src[rows][c_src]: extra channels are zero, surplus channels are dropped (channel
+ * padding of the image stem for the tensor-core convolution; no counterpart in the reference) */
+int mtb_resize_channels_f32(const float* src, float* dst, long long rows, int c_src, int c_dst, void* stream);
 int mtb_nchw_to_nhwc_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
 int mtb_nhwc_to_nchw_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
 /* kind: 0 int32->int64, 1 int64->float32, 2 float32->int64 (replaces cast_reference, cast.cu/source.cu:5-14) */

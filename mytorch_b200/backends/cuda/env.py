@@ -34,6 +34,7 @@ _SIGNATURES = {
     "mtb_mul_f32": ([_P, _P, _P, _L, _P], _I),
     "mtb_add_bias_rows_f32": ([_P, _P, _P, _L, _I, _F, _P], _I),
     "mtb_binary_strided_f32": ([_I, _I, _P, _P, _P, _P, _P, _P, _P, _F, _P], _I),
+    "mtb_resize_channels_f32": ([_P, _P, _L, _I, _I, _P], _I),
     "mtb_nchw_to_nhwc_f32": ([_P, _P, _I, _I, _I, _I, _P], _I),
     "mtb_nhwc_to_nchw_f32": ([_P, _P, _I, _I, _I, _I, _P], _I),
     "mtb_cast": ([_I, _P, _P, _L, _P], _I),

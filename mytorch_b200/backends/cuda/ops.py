@@ -52,6 +52,19 @@ def _new(shape, like, dtype=None):
     return _T()(shape=tuple(shape), dtype=dtype or like.dtype, device=like.device)
 
 
+def _grad_buffer(param):
+    """Output tensor for a parameter's gradient.  Under the data-parallel wrapper every parameter
+    owns a window of the flat all-reduce buffer (``param._grad_slot``) and its first gradient of a
+    backward pass is written straight into it; otherwise (no wrapper, or a second contribution that
+    the tape will add to the first) a fresh tensor."""
+    slot = getattr(param, "_grad_slot", None)
+    if slot is None or param.grad is not None:
+        return _new(param.shape, param)
+    g = _T()(tensor=param)
+    g._native_array = slot
+    return g
+
+
 def _f32(*tensors):
     from mytorch_b200.tensor import InvalidDataTypeError
 
@@ -129,9 +142,14 @@ def cuda_download(t):
 
 # ---------------------------------------------------------------------------- convolution
 
-def _conv_args(x, w, stride, padding):
-    n, cin, h, wd = x.shape
+def _conv_args(x, w, stride, padding, cin=None):
+    """(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout); `cin` overrides the filter's channel count when
+    the activation has been padded to a channel block but the filter has not."""
+    n, cin_x, h, wd = x.shape
     cout, cin2, kh, kw = w.shape
+    if cin is not None:
+        cin2 = cin
+    cin = cin_x
     if cin != cin2:
         from mytorch_b200.tensor import MismatchShapesError
 
@@ -152,21 +170,18 @@ def _wants_channel_padding(x):
 
 
 def _pad_channels(env, t, channels):
-    """Copy a channels-last tensor into a zero-filled one with `channels` channels (dim 1)."""
+    """A channels-last tensor copied into one with `channels` channels (dim 1), the new ones zero."""
     n, c, h, w = t.shape
     out = _new((n, channels, h, w), t)
-    env.lib.fill_f32(_ptr(out), _numel(out.shape), 0.0, env.stream())
-    src = _strides(t)
-    env.lib.binary_strided_f32(5, 4, _ll(t.shape), _ll(src), _ll(src), _ll(_strides(out)), _ptr(t), None, _ptr(out), 1.0, env.stream())
+    env.lib.resize_channels_f32(_ptr(t), _ptr(out), n * h * w, c, channels, env.stream())
     return out
 
 
-def _take_channels(env, t, channels, like):
-    """First `channels` channels (dim 1) of a channels-last tensor, as a new tensor."""
+def _take_channels(env, t, channels, like, out=None):
+    """First `channels` channels (dim 1) of a channels-last tensor, as a new tensor (or into `out`)."""
     n, c, h, w = t.shape
-    out = _new((n, channels, h, w), like)
-    src = _strides(t)
-    env.lib.binary_strided_f32(5, 4, _ll(out.shape), _ll(src), _ll(src), _ll(_strides(out)), _ptr(t), None, _ptr(out), 1.0, env.stream())
+    out = _new((n, channels, h, w), like) if out is None else out
+    env.lib.resize_channels_f32(_ptr(t), _ptr(out), n * h * w, c, channels, env.stream())
     return out
 
 
@@ -174,13 +189,15 @@ def _take_channels(env, t, channels, like):
 def cuda_conv2d(input, weight, bias, stride, padding):
     _f32(input, weight, bias)
     env = _env(input)
+    x, wt = input, weight
     if _wants_channel_padding(input):
-        input, weight = _pad_channels(env, input, _TC_CHANNELS), _pad_channels(env, weight, _TC_CHANNELS)
-    a = _conv_args(input, weight, stride, padding)
+        x, wt = _pad_channels(env, input, _TC_CHANNELS), _pad_channels(env, weight, _TC_CHANNELS)
+        input._padded_for_conv = x  # backward of this convolution reuses it (the weight gradient reads x again)
+    a = _conv_args(x, wt, stride, padding)
     n, cin, h, w, kh, kw, sh, sw, ph, pw, cout = a
     oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
     out = _new((n, cout, oh, ow), input)
-    env.lib.conv2d_forward_f32(*a, _ptr(input), _ptr(weight), _ptr(bias), _ptr(out), 0, env.stream())
+    env.lib.conv2d_forward_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, env.stream())
     return out
 
 
@@ -193,34 +210,44 @@ def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accu
     env = _env(input)
     want_dx, want_dw, cin = input.requires_grad, weight.requires_grad, input.shape[1]
     padded = _wants_channel_padding(input)
+    x, wt = input, weight
     if padded:
-        input, weight = _pad_channels(env, input, _TC_CHANNELS), _pad_channels(env, weight, _TC_CHANNELS)
-    a = _conv_args(input, weight, stride, padding)
+        x = getattr(input, "_padded_for_conv", None)
+        if x is None:
+            x = _pad_channels(env, input, _TC_CHANNELS)
+        else:
+            del input._padded_for_conv
+        if want_dx:  # the data gradient reads the (padded) filter; the weight gradient only needs its shape
+            wt = _pad_channels(env, weight, _TC_CHANNELS)
+    a = _conv_args(x, weight, stride, padding, cin=x.shape[1])
     st = env.stream()
     ws, ws_bytes = env.workspace(env.lib.conv2d_workspace_bytes(*a))
     dx = dw = db = None
     if want_dx:
-        dx = _new(input.shape, input)
+        dx = _new(x.shape, x)
         if accumulate_dx is not None and not padded:
-            env.lib.conv2d_dgrad_add_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(accumulate_dx), _ptr(dx), ws, ws_bytes, st)
+            env.lib.conv2d_dgrad_add_f32(*a, _ptr(output_grad), _ptr(wt), _ptr(accumulate_dx), _ptr(dx), ws, ws_bytes, st)
         else:
-            env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(weight), _ptr(dx), ws, ws_bytes, st)
+            env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(wt), _ptr(dx), ws, ws_bytes, st)
             if padded:
                 dx = _take_channels(env, dx, cin, dx)
             if accumulate_dx is not None:
                 dx = BackendDispatcher.instance().dispatch("cuda", "add")(dx, accumulate_dx, 1)
     if want_dw:
-        dw = _new(weight.shape, weight)
-        env.lib.conv2d_wgrad_f32(*a, _ptr(input), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)
         if padded:
-            dw = _take_channels(env, dw, cin, dw)
+            wide = _new((weight.shape[0], _TC_CHANNELS) + tuple(weight.shape[2:]), weight)
+            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(wide), ws, ws_bytes, st)
+            dw = _take_channels(env, wide, cin, weight, out=_grad_buffer(weight))
+        else:
+            dw = _grad_buffer(weight)
+            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)
     if bias is not None and bias.requires_grad:
-        db = _colsum(env, output_grad, _numel(output_grad.shape) // a[-1], a[-1], bias)
+        db = _colsum(env, output_grad, _numel(output_grad.shape) // a[-1], a[-1], bias, out=_grad_buffer(bias))
     return [dx, dw, db]
 
 
-def _colsum(env, mat, rows, cols, like, scale=1.0):
-    out = _new((cols,), like)
+def _colsum(env, mat, rows, cols, like, scale=1.0, out=None):
+    out = _new((cols,), like) if out is None else out
     ws, ws_bytes = env.workspace(env.lib.colsum_workspace_bytes(cols))
     env.lib.colsum_f32(_ptr(mat), rows, cols, scale, _ptr(out), ws, ws_bytes, env.stream())
     return out
@@ -257,10 +284,10 @@ def cuda_linear_backward(output_grad, x, weight, bias):
         dx = _new(x.shape, x)
         _gemm(env, b, fin, fout, output_grad, 0, weight, 0, None, 0, dx)
     if weight.requires_grad:
-        dw = _new(weight.shape, weight)
+        dw = _grad_buffer(weight)
         _gemm(env, fout, fin, b, output_grad, 1, x, 0, None, 0, dw)
     if bias is not None and bias.requires_grad:
-        db = _colsum(env, output_grad, b, fout, bias)
+        db = _colsum(env, output_grad, b, fout, bias, out=_grad_buffer(bias))
     return [dx, dw, db]
 
 
@@ -322,8 +349,8 @@ def cuda_batch_norm2d_backward(output_grad, mean, var, x, weight, bias, eps, rel
     n, c, h, w = x.shape
     dx = _new(x.shape, x)
     affine = weight is not None and bias is not None
-    dg = _new((c,), x) if affine else None
-    db = _new((c,), x) if affine else None
+    dg = _grad_buffer(weight) if affine else None
+    db = _grad_buffer(bias) if affine else None
     ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
     env.lib.batch_norm2d_backward_f32(n, c, h, w, _ptr(output_grad), _ptr(mean), _ptr(var), _ptr(x), _ptr(weight), _ptr(bias), float(eps),
                                       int(bool(relu)), _ptr(dx), _ptr(dg), _ptr(db), ws, ws_bytes, env.stream())

@@ -174,7 +174,28 @@ int transpose_planes(float* dst, const float* src, int batch, int rows, int cols
   return MTB_OK;
 }
 
+// dst[r][c] = c < c_src ? src[r][c] : 0 for c < c_dst: widen a [rows, c_src] matrix with zero
+// columns (c_dst > c_src) or keep its first c_dst columns (c_dst < c_src), in one pass.
+__global__ void __launch_bounds__(256) resize_channels_kernel(const float* __restrict__ src, float* __restrict__ dst, long long rows, int c_src, int c_dst) {
+  const long long total = rows * c_dst;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const long long r = i / c_dst;
+    const int c = (int)(i - r * c_dst);
+    dst[i] = c < c_src ? src[r * c_src + c] : 0.f;
+  }
+}
+
 }  // namespace
+
+// Copy a row-major [rows, c_src] matrix into [rows, c_dst]: extra columns are zero, surplus columns are
+// dropped.  Pads the 1- or 3-channel image stem (and its filter) to one 32-channel block for the
+// tensor-core convolution and cuts the weight gradient back; no counterpart in the reference.
+MTB_API int mtb_resize_channels_f32(const float* src, float* dst, long long rows, int c_src, int c_dst, void* stream) {
+  MTB_REQUIRE(src && dst && rows > 0 && c_src > 0 && c_dst > 0, "resize_channels: bad arguments");
+  resize_channels_kernel<<<mtb_stream_grid(rows * c_dst, kThreads), kThreads, 0, (cudaStream_t)stream>>>(src, dst, rows, c_src, c_dst);
+  MTB_LAUNCH_CHECK("resize_channels_kernel");
+  return MTB_OK;
+}
 
 MTB_API int mtb_fill_f32(float* x, long long n, float value, void* stream) {
   MTB_REQUIRE(n >= 0 && (x || n == 0), "fill: bad arguments");

@@ -248,6 +248,44 @@ MTB_API int mtb_conv2d_wgrad_simt_f32(int n, int cin, int h, int w, int kh, int 
   return MTB_OK;
 }
 
+// ------------------------------------------------------------------ few-row products (classifier weight gradient)
+
+namespace {
+
+// C[M,N] = A^T B for A stored [K][M] with M <= 16 and B [K][N]: the weight gradient of a Linear layer
+// with few outputs (dW[10][512] = dY^T X).  The 64x64-tile kernel above would run a handful of CTAs
+// that each walk all of K; here a CTA owns 32 columns, its 8 warps split K, every lane keeps M
+// accumulators for its column, and the 8 partial results are added in warp order through shared memory.
+__global__ void __launch_bounds__(256) gemm_few_rows_kernel(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ c,
+                                                             int M, int N, int K) {
+  __shared__ float part[8][16][33];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.x * 32 + lane;
+  float acc[16];
+#pragma unroll
+  for (int m = 0; m < 16; ++m) acc[m] = 0.f;
+  if (col < N) {
+    for (int k = warp; k < K; k += 8) {
+      const float bv = b[(long long)k * N + col];
+      const float* ar = a + (long long)k * M;
+#pragma unroll
+      for (int m = 0; m < 16; ++m)
+        if (m < M) acc[m] = fmaf(__ldg(ar + m), bv, acc[m]);
+    }
+  }
+#pragma unroll
+  for (int m = 0; m < 16; ++m) part[warp][m][lane] = acc[m];
+  __syncthreads();
+  for (int m = warp; m < M; m += 8) {
+    float t = part[0][m][lane];
+#pragma unroll
+    for (int w = 1; w < 8; ++w) t += part[w][m][lane];
+    if (col < N) c[(long long)m * N + col] = t;
+  }
+}
+
+}  // namespace
+
 // ------------------------------------------------------------------ dense GEMM (general path)
 
 // C[M,N] = op(A) * op(B) (+ bias[N]) (relu). A is [M,K] (trans_a == 0) or [K,M]; B is [K,N]
@@ -255,6 +293,11 @@ MTB_API int mtb_conv2d_wgrad_simt_f32(int n, int cin, int h, int w, int kh, int 
 MTB_API int mtb_gemm_simt_f32(int m, int n, int k, const float* a, int trans_a, const float* b, int trans_b, const float* bias, int relu,
                               float* c, void* stream) {
   MTB_REQUIRE(a && b && c && m > 0 && n > 0 && k > 0, "gemm: bad arguments");
+  if (trans_a && !trans_b && m <= 16 && !bias && !relu) {
+    gemm_few_rows_kernel<<<mtb_div_up(n, 32), 256, 0, (cudaStream_t)stream>>>(a, b, c, m, n, k);
+    MTB_LAUNCH_CHECK("gemm_few_rows_kernel");
+    return MTB_OK;
+  }
   Dense la = trans_a ? Dense{a, 1, m} : Dense{a, k, 1};
   Dense lb = trans_b ? Dense{b, k, 1} : Dense{b, 1, n};  // B(j, kk)
   StoreBias st{c, n, bias, relu};

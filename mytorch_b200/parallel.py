@@ -5,10 +5,14 @@ loop needs to run on 1/2/4/8 GPUs of one box.  The batch is split along dimensio
 rank holds a full replica (parameters, momentum buffers, BatchNorm running statistics), and
 BatchNorm uses the statistics of the local shard.
 
-After ``backward`` the gradients are gathered (and pre-scaled by 1/world) into one flat
-float32 buffer by a single multi-tensor kernel, all-reduced in place by NCCL over NVLink, and
-``param.grad`` is re-pointed at windows of that buffer, which the multi-tensor SGD kernel then
-reads in place.  With world size 1 nothing is copied or communicated.
+On CUDA every parameter owns a window of one flat float32 buffer per bucket, and the backward
+kernels (weight gradients, bias gradients, BatchNorm gradients) write ``param.grad`` straight
+into that window, so after ``backward`` the buffer is all-reduced in place by NCCL over NVLink
+(average) and the multi-tensor SGD kernel reads it in place: no gather or scatter copies.  A
+gradient that ended up elsewhere (a parameter used twice accumulates into a fresh tensor) is
+copied into its window first.  On the CPU (gloo, used by the tests) gradients are gathered into
+the flat buffer pre-scaled by 1/world and summed.  With world size 1 nothing is copied or
+communicated.
 """
 from __future__ import annotations
 
@@ -54,8 +58,18 @@ class GradBucket:
             self.flat = torch.zeros(self.total, dtype=torch.float32, device=where)
         return self.flat
 
+    def assign_slots(self):
+        """CUDA: give every parameter its window of the flat buffer (``param._grad_slot``); the
+        backward operators write the parameter's gradient there (``backends/cuda/ops.py``)."""
+        from mytorch_b200.backends.cuda.env import CudaMemoryView
+
+        raw = self._ensure_flat().view(dtype=__import__("torch").uint8)
+        for p, off, n in zip(self.params, self.offsets, self.sizes):
+            p._grad_slot = CudaMemoryView(raw[4 * off: 4 * (off + n)], p.device.index)
+
     def pack(self, scale, stream=None):
-        """flat[offset_k : offset_k + n_k] = scale * grad_k for every parameter."""
+        """CPU: flat[offset_k : offset_k + n_k] = scale * grad_k for every parameter.  CUDA: the same
+        copy (scale 1), but only for gradients that do not already live in their window."""
         flat = self._ensure_flat()
         if self.params[0].device.type == "cpu":
             view = flat.numpy()
@@ -64,12 +78,15 @@ class GradBucket:
             return flat
         from mytorch_b200.backends.cuda.env import CudaEnv
 
-        env = CudaEnv.instance()
-        k = len(self.params)
-        srcs = (ctypes.c_void_p * k)(*[p.grad._native_array.ptr for p in self.params])
-        offs = (ctypes.c_longlong * k)(*self.offsets)
-        sizes = (ctypes.c_longlong * k)(*self.sizes)
-        env.lib.pack_scale_f32(k, srcs, offs, sizes, flat.data_ptr(), float(scale), env.stream() if stream is None else stream)
+        stray = [(p, off, n) for p, off, n in zip(self.params, self.offsets, self.sizes)
+                 if p.grad._native_array.ptr != p._grad_slot.ptr]
+        if stray:
+            env = CudaEnv.instance()
+            k = len(stray)
+            srcs = (ctypes.c_void_p * k)(*[p.grad._native_array.ptr for p, _, _ in stray])
+            offs = (ctypes.c_longlong * k)(*[off for _, off, _ in stray])
+            sizes = (ctypes.c_longlong * k)(*[n for _, _, n in stray])
+            env.lib.pack_scale_f32(k, srcs, offs, sizes, flat.data_ptr(), float(scale), env.stream() if stream is None else stream)
         return flat
 
     def point_grads_at_flat(self):
@@ -80,13 +97,11 @@ class GradBucket:
             for p, off, n in zip(self.params, self.offsets, self.sizes):
                 p.grad = Tensor(cpu_array=view[off:off + n].reshape(p.shape))
             return
-        from mytorch_b200.backends.cuda.env import CudaMemoryView
-
-        raw = flat.view(dtype=__import__("torch").uint8)
-        for p, off, n in zip(self.params, self.offsets, self.sizes):
-            g = Tensor(tensor=p.grad)
-            g._native_array = CudaMemoryView(raw[4 * off: 4 * (off + n)], p.device.index)
-            p.grad = g
+        for p in self.params:
+            if p.grad._native_array.ptr != p._grad_slot.ptr:  # it was copied into the window by pack()
+                g = Tensor(tensor=p.grad)
+                g._native_array = p._grad_slot
+                p.grad = g
 
 
 def split_into_buckets(params, count):
@@ -122,12 +137,16 @@ class DataParallel:
         self.world = dist.get_world_size(process_group) if dist.is_available() and dist.is_initialized() else 1
         self.rank = dist.get_rank(process_group) if self.world > 1 else 0
         self.buckets, self._bucket_of, self._remaining, self._events = [], {}, [], []
-        self._side = None
+        self._side, self._on_cuda = None, False
         if self.world > 1:
             params = list(module.parameters())
             on_cuda = params[0].device.type == "cuda"
             groups = split_into_buckets(params, buckets)
             self.buckets = [GradBucket(g) for g in groups]
+            self._on_cuda = on_cuda
+            if on_cuda:
+                for b in self.buckets:
+                    b.assign_slots()
             for b, g in enumerate(groups):
                 for p in g:
                     self._bucket_of[id(p)] = b
@@ -159,16 +178,22 @@ class DataParallel:
         import torch.distributed as dist
 
         bucket = self.buckets[b]
-        if stream is None:
+        if not self._on_cuda:
             flat = bucket.pack(1.0 / self.world)
             dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            return
+        # gradients already sit in the flat buffer; 1/world is an exact scaling for the power-of-two
+        # world sizes of one box, so NCCL's average equals the sum of pre-scaled gradients bit for bit
+        if stream is None:
+            flat = bucket.pack(1.0)
+            dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
             return
         ready = torch.cuda.Event()
         ready.record(torch.cuda.current_stream())
         with torch.cuda.stream(stream):
             stream.wait_event(ready)
-            flat = bucket.pack(1.0 / self.world, stream=stream.cuda_stream)
-            dist.all_reduce(flat, op=dist.ReduceOp.SUM, group=self.group)
+            flat = bucket.pack(1.0, stream=stream.cuda_stream)
+            dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
             done = torch.cuda.Event()
             done.record(stream)
         self._events[b] = done
