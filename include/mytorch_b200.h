@@ -46,6 +46,16 @@ long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int k
 /* y[N,OH,OW,Cout] = conv(x[N,H,W,Cin], wt[Cout,KH,KW,Cin]) + bias (bias may be NULL); relu != 0 clamps at 0 */
 int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                            const float* wt, const float* bias, float* y, int relu, void* stream);
+/* The same forward pass for a convolution whose output feeds a BatchNorm layer: where the kernel family
+ * allows, the epilogue also reduces per-channel batch statistics of y from the accumulator rows it
+ * already holds, so BatchNorm's own statistics pass (a full re-read of y) can be skipped.  stats: room
+ * for mtb_conv2d_stats_max_rows() * 3 * cout floats.  *stats_rows (HOST pointer) receives the number of
+ * partial rows [row][3][cout] = (count, mean, M2) written, or 0 when this shape produced none (run the
+ * ordinary BatchNorm forward then).  Fuses the seam between mytorch/nn/conv.py:71 and
+ * mytorch/nn/batch_norm.py:123-135; no counterpart in the reference. */
+int mtb_conv2d_stats_max_rows(void);
+int mtb_conv2d_forward_stats_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                 const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* stream);
 /* dx[N,H,W,Cin]: every element is written (zeros where no window reaches); no atomics */
 int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                          const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream);
@@ -76,6 +86,10 @@ long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w);
 int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps, int training,
                                  double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var, int relu,
                                  void* workspace, long long workspace_bytes, void* stream);
+/* training-mode forward from statistics partials prepared by mtb_conv2d_forward_stats_f32 (stats_rows > 0) */
+int mtb_batch_norm2d_forward_prestats_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps,
+                                          double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var,
+                                          int relu, const float* stats, int stats_rows, void* workspace, long long workspace_bytes, void* stream);
 /* relu != 0 in forward fuses max(0, .) into the normalise pass; the same flag in backward masks dy where
  * gamma*xhat + beta < 0 (recomputed, so the ReLU output need not be kept).  beta may be NULL (= 0). */
 int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,

@@ -61,6 +61,9 @@ _SIGNATURES = {
     "mtb_conv2d_workspace_bytes": (_CONV, _L),
     "mtb_conv2d_plan_f32": (_CONV + [_P], _I),
     "mtb_conv2d_forward_f32": (_CONV + [_P, _P, _P, _P, _I, _P], _I),
+    "mtb_conv2d_stats_max_rows": ([], _I),
+    "mtb_conv2d_forward_stats_f32": (_CONV + [_P, _P, _P, _P, _I, _P, _P, _P], _I),
+    "mtb_batch_norm2d_forward_prestats_f32": ([_I, _I, _I, _I, _P, _P, _P, _D, _D, _P, _P, _P, _P, _P, _I, _P, _I, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_add_f32": (_CONV + [_P, _P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_wgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
@@ -95,7 +98,7 @@ class NativeLibrary:
             fn = getattr(self._dll, name)
             fn.argtypes = argtypes
             fn.restype = restype
-            setattr(self, name[4:], self._checked(name, fn) if restype is _I and name not in ("mtb_version",) else fn)
+            setattr(self, name[4:], self._checked(name, fn) if restype is _I and name not in ("mtb_version", "mtb_conv2d_stats_max_rows") else fn)
 
     def _checked(self, name, fn):
         def call(*args):

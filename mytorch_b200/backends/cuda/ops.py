@@ -186,7 +186,10 @@ def _take_channels(env, t, channels, like, out=None):
 
 
 @_reg("cuda", "conv2d")
-def cuda_conv2d(input, weight, bias, stride, padding):
+def cuda_conv2d(input, weight, bias, stride, padding, bn_stats=False):
+    """``bn_stats``: the output feeds a BatchNorm layer in training mode; where the kernel allows, the
+    convolution's epilogue also reduces the per-channel batch statistics of the output and leaves them
+    on the result (``_bn_partials``) for ``batch_norm2d``, which then skips its own pass over the tensor."""
     _f32(input, weight, bias)
     env = _env(input)
     x, wt = input, weight
@@ -197,6 +200,13 @@ def cuda_conv2d(input, weight, bias, stride, padding):
     n, cin, h, w, kh, kw, sh, sw, ph, pw, cout = a
     oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
     out = _new((n, cout, oh, ow), input)
+    if bn_stats:
+        partials = CudaMemory(input.device.index, env.lib.conv2d_stats_max_rows() * 3 * cout * 4)
+        rows = ctypes.c_int(0)
+        env.lib.conv2d_forward_stats_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, partials.ptr, ctypes.byref(rows), env.stream())
+        if rows.value > 0:
+            out._bn_partials = (partials, rows.value)
+        return out
     env.lib.conv2d_forward_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, env.stream())
     return out
 
@@ -327,6 +337,12 @@ def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, ru
     # without running statistics the reference normalises with batch statistics in eval mode too
     # (``mytorch/backends/cpu/ops/batch_norm.py:40-46``)
     use_batch_stats = bool(training) or running_mean is None or running_var is None
+    pre = getattr(x, "_bn_partials", None)
+    if use_batch_stats and pre is not None:  # the convolution that produced x already reduced its statistics
+        env.lib.batch_norm2d_forward_prestats_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), float(momentum), _ptr(running_mean),
+                                                  _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), int(bool(relu)), pre[0].ptr, pre[1], ws, ws_bytes,
+                                                  env.stream())
+        return y, mean, var
     env.lib.batch_norm2d_forward_f32(n, c, h, w, _ptr(x), _ptr(weight), _ptr(bias), float(eps), int(use_batch_stats), float(momentum),
                                      _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var), int(bool(relu)), ws, ws_bytes, env.stream())
     return y, mean, var

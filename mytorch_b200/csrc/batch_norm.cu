@@ -342,6 +342,21 @@ ColCfg stream_cfg(long long rows, int C, bool aligned) {
   return c;
 }
 
+int launch_normalize(const float* x, float* y, long long rows, int c, bool aligned, const float* mean, const float* scale, const float* beta,
+                     int relu, cudaStream_t st) {
+  ColCfg s = stream_cfg(rows, c, aligned);
+  dim3 grid(s.col_blocks, s.row_blocks);
+  if (s.vec == 4) {
+    if (relu) bn_normalize_kernel<4, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+    else bn_normalize_kernel<4, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+  } else {
+    if (relu) bn_normalize_kernel<1, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+    else bn_normalize_kernel<1, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
+  }
+  MTB_LAUNCH_CHECK("bn_normalize_kernel");
+  return MTB_OK;
+}
+
 }  // namespace
 
 // Scratch the forward and backward entry points need, in bytes (an upper bound for the shape).
@@ -379,17 +394,27 @@ MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float
     bn_eval_prep_kernel<<<fin_blocks, 128, 0, st>>>(c, gamma, (float)eps, running_mean, running_var, mean, var, scale);
     MTB_LAUNCH_CHECK("bn_eval_prep_kernel");
   }
-  ColCfg s = stream_cfg(rows, c, aligned);
-  dim3 grid(s.col_blocks, s.row_blocks);
-  if (s.vec == 4) {
-    if (relu) bn_normalize_kernel<4, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-    else bn_normalize_kernel<4, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-  } else {
-    if (relu) bn_normalize_kernel<1, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-    else bn_normalize_kernel<1, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-  }
-  MTB_LAUNCH_CHECK("bn_normalize_kernel");
-  return MTB_OK;
+  return launch_normalize(x, y, rows, c, aligned, mean, scale, beta, relu, st);
+}
+
+// Training-mode forward whose batch statistics were prepared by the producer of x: `stats` holds
+// stats_rows partial rows [row][3][C] of per-channel (count, mean, M2) that together cover every element
+// of x exactly once (mtb_conv2d_forward_stats_f32 writes them from the convolution's epilogue).  The
+// statistics pass over x is skipped: the partials are merged (fixed order), then x is normalised.
+MTB_API int mtb_batch_norm2d_forward_prestats_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps,
+                                                  double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var,
+                                                  int relu, const float* stats, int stats_rows, void* workspace, long long workspace_bytes,
+                                                  void* stream) {
+  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && x && y && mean && var && workspace && stats && stats_rows > 0,
+              "batch_norm2d_forward_prestats: bad arguments");
+  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_forward_prestats: workspace too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long rows = (long long)n * h * w;
+  float* scale = (float*)workspace + (long long)mtb_col_max_partials() * 3 * c;
+  bn_stats_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(stats, stats_rows, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+                                                            running_mean, running_var, mean, var, scale);
+  MTB_LAUNCH_CHECK("bn_stats_final_kernel");
+  return launch_normalize(x, y, rows, c, mtb_aligned16(x) && mtb_aligned16(y), mean, scale, beta, relu, st);
 }
 
 // dx = gamma/sigma * (dy - dbeta/m - xhat * dgamma/m); dgamma, dbeta may be NULL (not affine).

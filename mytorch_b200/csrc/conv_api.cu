@@ -17,6 +17,23 @@ MTB_API int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw,
   return mtb_conv2d_forward_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
 }
 
+// Forward convolution that also prepares the batch statistics of its output for a BatchNorm layer
+// that follows (the statistics pass of BatchNorm re-reads the whole activation otherwise).  stats:
+// room for mtb_conv2d_stats_max_rows() x 3 x cout floats; *stats_rows (HOST) receives the number of
+// partial rows [row][3][cout] = (count, mean, M2) written, to be passed to
+// mtb_batch_norm2d_forward_prestats_f32, or 0 when this shape's kernel does not produce them (the
+// caller then runs the ordinary BatchNorm forward).
+MTB_API int mtb_conv2d_stats_max_rows() { return 4 * mtb_sm_count(); }
+
+MTB_API int mtb_conv2d_forward_stats_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
+                                         const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* stream) {
+  MTB_REQUIRE(stats && stats_rows, "conv2d_forward_stats: stats buffer and row counter are required");
+  *stats_rows = 0;
+  if (mtb_tc_conv2d_forward_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, y))
+    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream, stats, stats_rows);
+  return mtb_conv2d_forward_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
+}
+
 MTB_API int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                                  const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream) {
   if (mtb_tc_conv2d_dgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx))

@@ -207,6 +207,110 @@ __host__ __device__ constexpr uint32_t idesc_tf32(int m, int n, int a_mn_major, 
          ((uint32_t)(m >> 4) << 24);
 }
 
+// ---- per-channel statistics of the rows an epilogue warp holds ----
+//
+// An epilogue warp owns 32 output rows (one per lane) and walks the tile's columns in chunks of 32:
+// lane i holds v[0..31] = row i, columns c0..c0+31.  warp_transpose_sum adds the 32 lanes' arrays
+// column-wise and leaves the sum of column j in lane j (five exchange steps: a lane keeps one half of
+// its array and receives the partner's sums for that half).  The array is consumed.
+__device__ __forceinline__ float warp_transpose_sum(float (&v)[32], int lane) {
+#pragma unroll
+  for (int half = 16; half >= 1; half >>= 1) {
+    const bool upper = (lane & half) != 0;
+#pragma unroll
+    for (int k = 0; k < half; ++k) {
+      const float keep = upper ? v[k + half] : v[k];
+      const float send = upper ? v[k] : v[k + half];
+      v[k] = keep + __shfl_xor_sync(0xffffffffu, send, half);
+    }
+  }
+  return v[0];
+}
+
+// Running (count, mean, M2) of CHUNKS x 32 columns over all rows a warp has seen; lane j owns column
+// j of every chunk.  A tile contributes its mean and centred sum of squares (two column sums over the
+// warp's valid rows), merged with Chan's update, so nothing is lost to cancellation when the mean is
+// large against the spread.  The convolution epilogues use it to hand BatchNorm its batch statistics
+// without a second pass over the output.
+template <int CHUNKS>
+struct WarpColStats {
+  float n, mean[CHUNKS], m2[CHUNKS];
+  __device__ __forceinline__ void reset() {
+    n = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) { mean[c] = 0.f; m2[c] = 0.f; }
+  }
+  // o: this lane's row, 32 columns of chunk `c` (compile-time after unrolling); cnt = valid rows in the warp
+  __device__ __forceinline__ void add_chunk(int c, const float (&o)[32], bool valid, float cnt, int lane) {
+    float t[32];
+#pragma unroll
+    for (int k = 0; k < 32; ++k) t[k] = valid ? o[k] : 0.f;
+    const float mt = warp_transpose_sum(t, lane) / cnt;
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const float d = o[k] - __shfl_sync(0xffffffffu, mt, k);
+      t[k] = valid ? d * d : 0.f;
+    }
+    const float q = warp_transpose_sum(t, lane);
+    const float wb = cnt / (n + cnt);
+    const float d = mt - mean[c];
+    mean[c] += d * wb;
+    m2[c] += q + d * d * n * wb;
+  }
+  // one partial row [3][C] (count, mean, M2) at columns col0 + 32 c + lane
+  __device__ __forceinline__ void store(float* row, int C, int col0, int ncols, int lane) const {
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const int col = col0 + 32 * c + lane;
+      if (col < ncols) { row[col] = n; row[C + col] = mean[c]; row[2 * C + col] = m2[c]; }
+    }
+  }
+};
+
+// The cheap form for narrow tiles (64 columns), whose main loop per tile is short enough that every
+// instruction an epilogue warp issues is felt by the MMA-issuing warp on the same scheduler: each lane
+// keeps plain sums and sums of squares of ITS rows, column by column, in registers (two FADD/FFMA per
+// element, no exchange), and the 32 lanes are combined once, when the CTA has finished its tiles.  The
+// sums are taken of the raw accumulator, i.e. of y - bias: the bias is the natural pivot of a
+// convolution's output, so the single-pass variance loses accuracy only as (mean - bias)^2 / var grows
+// (relative error about 6e-8 * (1 + that ratio) * sqrt(rows per lane)).
+template <int CHUNKS>
+struct LaneColSums {
+  float cnt, s1[CHUNKS][32], s2[CHUNKS][32];
+  __device__ __forceinline__ void reset() {
+    cnt = 0.f;
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c)
+#pragma unroll
+      for (int k = 0; k < 32; ++k) { s1[c][k] = 0.f; s2[c][k] = 0.f; }
+  }
+  __device__ __forceinline__ void add_chunk(int c, const uint32_t (&r)[32]) {  // raw accumulator row of a valid pixel
+#pragma unroll
+    for (int k = 0; k < 32; ++k) {
+      const float v = __uint_as_float(r[k]);
+      s1[c][k] += v;
+      s2[c][k] = fmaf(v, v, s2[c][k]);
+    }
+  }
+  // one partial row [3][C] (count, mean, M2); bias (may be NULL) is added back to the mean
+  __device__ __forceinline__ void store(float* row, int C, int col0, int ncols, const float* bias, int lane) {
+    float n = cnt;
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) n += __shfl_xor_sync(0xffffffffu, n, off);
+#pragma unroll
+    for (int c = 0; c < CHUNKS; ++c) {
+      const float t1 = warp_transpose_sum(s1[c], lane), t2 = warp_transpose_sum(s2[c], lane);
+      const int col = col0 + 32 * c + lane;
+      if (col < ncols) {
+        const float mu = n > 0.f ? t1 / n : 0.f;
+        row[col] = n;
+        row[C + col] = mu + (bias ? bias[col] : 0.f);
+        row[2 * C + col] = n > 0.f ? fmaxf(t2 - t1 * mu, 0.f) : 0.f;
+      }
+    }
+  }
+};
+
 // ---- host: tensor maps ----
 // fp32 matrix [rows][cols] row-major (row pitch `pitch_elems`), boxes of box_cols x box_rows
 // elements, 128-byte swizzle, zero fill outside the matrix.

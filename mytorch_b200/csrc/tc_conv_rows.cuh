@@ -40,6 +40,9 @@ struct RowConvParams {
   const float* addend;     // optional [same shape as out]: out = conv + addend (gradient accumulation)
   int relu;
   int b_tap_x[64];         // MN-major B only: first column of tap j in the weight matrix
+  // STATS kernels only: partial rows [(blockIdx.x / n_tiles) * 4 + epilogue warp][3][N] of per-channel
+  // (count, mean, M2) over the pixels this CTA produced (grid is a multiple of n_tiles)
+  float* stats;
 };
 
 constexpr uint32_t kRowLead = 1024;  // room for the left-most tap of the first position to reach back
@@ -53,7 +56,7 @@ constexpr int kRowAStages = 2;
 // MT = tiles of 128 positions per work item.  With streamed weights two tiles share every weight
 // stage (two accumulators), which halves the L2 -> shared-memory weight traffic per MMA; that traffic,
 // at ~47 B/cycle/SM, is what bounds the 128-channel layers.
-template <int BN, int BMODE, int FK, int MT>
+template <int BN, int BMODE, int FK, int MT, bool STATS>
 __global__ void __launch_bounds__(192, 1)
 tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const RowConvParams p) {
   constexpr uint32_t kTapBytes = BN * 128;
@@ -296,6 +299,11 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     int t = 0;
     const bool vec_ok = (p.ldo % 4 == 0) &&
                         (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.addend)) & 15u) == 0);
+    // statistics variant: narrow tiles keep per-lane sums (cheap per tile), wide tiles merge per tile
+    constexpr bool LANE_SUMS = STATS && BN == 64;
+    WarpColStats<(STATS && !LANE_SUMS) ? BN / 32 : 1> stats;
+    LaneColSums<LANE_SUMS ? BN / 32 : 1> sums;
+    if constexpr (LANE_SUMS) sums.reset(); else stats.reset();
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
       const int q_item = (tile / p.n_tiles) * (128 * MT) + quarter * 32 + lane;
       const int n0 = (tile % p.n_tiles) * BN;
@@ -328,6 +336,41 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (STATS) {
+        // forward convolution feeding a BatchNorm layer (no addend, N % 32 == 0, aligned: checked on the
+        // host): store the rows and fold them into the per-channel statistics
+#pragma unroll
+        for (int m = 0; m < MT; ++m) {
+          float* orow = p.out + ooff[m];
+          const float cnt = (float)__popc(__ballot_sync(0xffffffffu, valid[m]));
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)((buf * MT + m) * BN + c0), r);
+            tmem_ld_wait();
+            const int col0 = n0 + c0;
+            if (col0 < p.N) {  // warp-uniform
+              float o[32];
+#pragma unroll
+              for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + col0 + j) : 0.f);
+              if (valid[m]) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + col0 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+              }
+              if constexpr (LANE_SUMS) {
+                if (valid[m]) sums.add_chunk(c0 / 32, r);
+              } else {
+                if (cnt > 0.f) stats.add_chunk(c0 / 32, o, valid[m], cnt, lane);
+              }
+            }
+          }
+          if constexpr (LANE_SUMS) sums.cnt += valid[m] ? 1.f : 0.f; else stats.n += cnt;
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+        continue;
+      }
 #pragma unroll
       for (int m = 0; m < MT; ++m) {
         float* orow = p.out + ooff[m];
@@ -372,6 +415,11 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+    }
+    if constexpr (STATS) {
+      float* row = p.stats + ((long long)(blockIdx.x / p.n_tiles) * 4 + quarter) * 3 * p.N;
+      if constexpr (LANE_SUMS) sums.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, p.bias, lane);
+      else stats.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, lane);
     }
   }
 
@@ -448,17 +496,30 @@ RowConvPlan row_conv_plan(int n, int h, int w, int kh, int kw, int sh, int sw, i
   return r;
 }
 
-template <int BN, int BMODE, int FK, int MT>
-int launch_row_conv(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
-  auto kernel = tc_conv_rows_kernel<BN, BMODE, FK, MT>;
+template <int BN, int BMODE, int FK, int MT, bool STATS>
+int launch_row_conv_kernel(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
+  auto kernel = tc_conv_rows_kernel<BN, BMODE, FK, MT, STATS>;
   static unsigned long long configured = 0;
   if (int rc = mtb_opt_in_smem((const void*)kernel, 227 * 1024 - 1024, &configured)) return rc;
   const int items = ((p.m_tiles + MT - 1) / MT) * p.n_tiles;
-  const int grid = items < mtb_sm_count() ? items : mtb_sm_count();
+  int grid = items < mtb_sm_count() ? items : mtb_sm_count();
+  if (STATS) grid = grid / p.n_tiles * p.n_tiles;  // every CTA stays on one output-channel tile
   kernel<<<grid, 192, smem_bytes, st>>>(mapA, mapB, p);
   MTB_LAUNCH_CHECK("tc_conv_rows_kernel");
   return MTB_OK;
 }
+
+// the statistics variant exists for the forward role only (K-major weights)
+template <int BN, int BMODE, int FK, int MT>
+int launch_row_conv(const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
+  if constexpr (BMODE == B_KMAJOR) {
+    if (p.stats) return launch_row_conv_kernel<BN, BMODE, FK, MT, true>(mapA, mapB, p, smem_bytes, st);
+  }
+  return launch_row_conv_kernel<BN, BMODE, FK, MT, false>(mapA, mapB, p, smem_bytes, st);
+}
+
+// Partial-statistics rows the STATS variant writes (see RowConvParams::stats).
+int row_conv_stats_rows(const RowConvPlan& plan, long long positions, int nout, int bn);
 
 template <int BMODE>
 int launch_row_conv_bn(int bn, int mt, const CUtensorMap& mapA, const CUtensorMap& mapB, const RowConvParams& p, uint32_t smem_bytes, cudaStream_t st) {
@@ -477,7 +538,8 @@ int launch_row_conv_bn(int bn, int mt, const CUtensorMap& mapA, const CUtensorMa
 // act: [N, H, W, kc] channels-last; out: [N, H, W, nout].
 template <int BMODE>
 int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, int kh, int kw, int ph, int pw, int nout, const float* act,
-                 const CUtensorMap& mapB, const int* b_tap_x, const float* bias, const float* addend, int relu, float* out, cudaStream_t st) {
+                 const CUtensorMap& mapB, const int* b_tap_x, const float* bias, const float* addend, int relu, float* out, cudaStream_t st,
+                 float* stats = nullptr) {
   CUtensorMap mapA;
   int rc = tc::encode_rows_4d(&mapA, act, n, h, w, kc, 32, plan.Wp);
   if (rc) return rc;
@@ -488,8 +550,17 @@ int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, i
   p.m_tiles = (int)((p.Q + 127) / 128); p.n_tiles = (nout + bn - 1) / bn;
   p.a_stage_bytes = plan.a_stage_bytes; p.b_stages = plan.b_stages; p.tps = plan.tps; p.resident = plan.resident;
   p.out = out; p.ldo = nout; p.bias = bias; p.addend = addend; p.relu = relu;
+  p.stats = stats;
   if (b_tap_x) for (int j = 0; j < kh * kw; ++j) p.b_tap_x[j] = b_tap_x[j];
   return launch_row_conv_bn<BMODE>(bn, plan.mt, mapA, mapB, p, plan.smem_bytes, st);
+}
+
+int row_conv_stats_rows(const RowConvPlan& plan, long long positions, int nout, int bn) {
+  const long long m_tiles = (positions + 127) / 128;
+  const int n_tiles = (nout + bn - 1) / bn;
+  const long long items = ((m_tiles + plan.mt - 1) / plan.mt) * n_tiles;
+  const int grid = (int)(items < mtb_sm_count() ? items : mtb_sm_count());
+  return grid / n_tiles * 4;
 }
 
 }  // namespace

@@ -118,6 +118,10 @@ struct GemmParams {
   // Output rows are pixels of a strided sub-grid of an [N, o_H, o_W, ldo] tensor: row
   // (n, i, j) of an o_Hc x o_Wc grid lands on pixel (o_h0 + o_sh*i, o_w0 + o_sw*j).
   int o_strided, o_Hc, o_Wc, o_H, o_W, o_h0, o_w0, o_sh, o_sw;
+  // STATS kernels only: partial rows [(blockIdx.x / n_tiles) * 4 + epilogue warp][3][N] of per-column
+  // (count, mean, M2) over the output rows this CTA produced (the grid is a multiple of n_tiles, so a
+  // CTA always works on the same column tile)
+  float* stats;
 };
 
 // A stage holds kKB reduction blocks of 32 (each one 128-byte swizzle span per operand row).  One
@@ -135,7 +139,7 @@ struct Cfg {
   static constexpr uint32_t kTmemCols = 2 * BN;
 };
 
-template <int BN, int AMODE, int BMODE>
+template <int BN, int AMODE, int BMODE, bool STATS>
 __global__ void __launch_bounds__(192, 1)
 tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const GemmParams p) {
   using C = Cfg<BN>;
@@ -282,6 +286,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int quarter = warp & 3;
     int t = 0;
     const bool vec_ok = (p.ldo % 4 == 0) && (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias)) & 15u) == 0);
+    // statistics variant: narrow tiles keep per-lane sums (cheap per tile), wide tiles merge per tile
+    constexpr bool LANE_SUMS = STATS && BN == 64;
+    WarpColStats<(STATS && !LANE_SUMS) ? BN / 32 : 1> stats;
+    LaneColSums<LANE_SUMS ? BN / 32 : 1> sums;
+    if constexpr (LANE_SUMS) sums.reset(); else stats.reset();
     for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
       const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
       const int buf = t & 1;
@@ -299,6 +308,38 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         orow_index = ((long long)nn * p.o_H + p.o_h0 + p.o_sh * i) * p.o_W + p.o_w0 + p.o_sw * j;
       }
       float* orow = p.out + orow_index * p.ldo;
+      if constexpr (STATS) {
+        // the forward convolution that feeds a BatchNorm layer: full column tiles (N % 32 == 0, checked on
+        // the host), vector stores, and the per-channel statistics of what is stored
+        const bool valid = row < p.M;
+        const float cnt = (float)__popc(__ballot_sync(0xffffffffu, valid));
+#pragma unroll
+        for (int c0 = 0; c0 < BN; c0 += 32) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+          tmem_ld_wait();
+          const int col0 = n0 + c0;
+          if (col0 < p.N) {  // warp-uniform
+            float o[32];
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + col0 + j) : 0.f);
+            if (valid) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + col0 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+            }
+            if constexpr (LANE_SUMS) {
+              if (valid) sums.add_chunk(c0 / 32, r);
+            } else {
+              if (cnt > 0.f) stats.add_chunk(c0 / 32, o, valid, cnt, lane);
+            }
+          }
+        }
+        if constexpr (LANE_SUMS) sums.cnt += valid ? 1.f : 0.f; else stats.n += cnt;
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
@@ -334,6 +375,11 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
     }
+    if constexpr (STATS) {
+      float* row = p.stats + ((long long)(blockIdx.x / p.n_tiles) * 4 + quarter) * 3 * p.N;
+      if constexpr (LANE_SUMS) sums.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, p.bias, lane);
+      else stats.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, lane);
+    }
   }
 
   // ------------------------------------------------------------ teardown
@@ -349,17 +395,24 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   }
 }
 
-template <int BN, int AMODE, int BMODE>
+template <int BN, int AMODE, int BMODE, bool STATS = false>
 int launch_tc(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams& p, cudaStream_t st) {
   using C = Cfg<BN>;
-  auto kernel = tc_gemm_kernel<BN, AMODE, BMODE>;
+  auto kernel = tc_gemm_kernel<BN, AMODE, BMODE, STATS>;
   static unsigned long long configured = 0;
   if (int rc = mtb_opt_in_smem((const void*)kernel, (int)C::kSmemBytes, &configured)) return rc;
   int tiles = p.m_tiles * p.n_tiles;
   int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
+  if (STATS) grid = grid / p.n_tiles * p.n_tiles;  // every CTA stays on one column tile (see GemmParams::stats)
   kernel<<<grid, 192, C::kSmemBytes, st>>>(mapA, mapB, p);
   MTB_LAUNCH_CHECK("tc_gemm_kernel");
   return MTB_OK;
+}
+
+// Partial-statistics rows the STATS variant writes for a problem of `tiles` tiles in `n_tiles` column tiles.
+int stats_rows_for(int tiles, int n_tiles) {
+  int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
+  return grid / n_tiles * 4;
 }
 
 template <int AMODE, int BMODE>
@@ -490,16 +543,25 @@ bool mtb_tc_conv2d_forward_supported(int n, int cin, int h, int w, int kh, int k
   return true;
 }
 
+// stats / stats_rows (both may be NULL): when given and the shape allows, the kernel also writes partial
+// rows [rows][3][cout] of per-channel (count, mean, M2) of y and *stats_rows receives their number;
+// *stats_rows == 0 means this launch did not produce statistics.
 int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                              const float* wt, const float* bias, float* y, int relu, void* stream) {
+                              const float* wt, const float* bias, float* y, int relu, void* stream, float* stats, int* stats_rows) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   const long long M = (long long)n * oh * ow, K = (long long)kh * kw * cin;
   const int bn = pick_bn_for(cout, M);
+  if (stats_rows) *stats_rows = 0;
+  const bool want_stats = stats && stats_rows && !relu && cout % 32 == 0 && (!bias || al16(bias)) && !getenv("MTB_DISABLE_CONV_STATS");
   CUtensorMap mapA, mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, K, K, 32, bn);
   if (rc) return rc;
   const RowConvPlan plan = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, cin, cout, bn);
-  if (plan.ok) return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, nullptr, relu, y, (cudaStream_t)stream);
+  if (plan.ok) {
+    if (want_stats) *stats_rows = row_conv_stats_rows(plan, (long long)n * plan.Hv * plan.Wp, cout, bn);
+    return run_row_conv<B_KMAJOR>(plan, bn, n, h, w, cin, kh, kw, ph, pw, cout, x, mapB, nullptr, bias, nullptr, relu, y, (cudaStream_t)stream,
+                                  want_stats ? stats : nullptr);
+  }
   rc = tc::encode_im2col_4d(&mapA, x, n, h, w, cin, -pw, -ph, pw - (kw - 1), ph - (kh - 1), sw, sh, 32, 128);
   if (rc) return rc;
   GemmParams p{};
@@ -507,6 +569,15 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
   p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cout + bn - 1) / bn;
   p.out = y; p.ldo = cout; p.bias = bias; p.relu = relu;
   p.OW = ow; p.OH = oh; p.SW = sw; p.SH = sh; p.PW = pw; p.PH = ph; p.KW = kw; p.KH = kh; p.cchunks = cin / 32;
+  // short reductions (1x1 shortcuts) leave the epilogue no main loop to hide the statistics behind
+  if (want_stats && p.num_kb >= 16 && p.m_tiles * p.n_tiles >= p.n_tiles) {
+    p.stats = stats;
+    *stats_rows = stats_rows_for(p.m_tiles * p.n_tiles, p.n_tiles);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (bn == 64) return launch_tc<64, A_IM2COL, B_KMAJOR, true>(mapA, mapB, p, st);
+    if (bn == 128) return launch_tc<128, A_IM2COL, B_KMAJOR, true>(mapA, mapB, p, st);
+    return launch_tc<256, A_IM2COL, B_KMAJOR, true>(mapA, mapB, p, st);
+  }
   return launch_tc_bn<A_IM2COL, B_KMAJOR>(bn, mapA, mapB, p, (cudaStream_t)stream);
 }
 

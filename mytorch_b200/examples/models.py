@@ -26,11 +26,18 @@ def _bn_relu(channels, fused, device):
     return (nn.BatchNormReLU2d(channels, device=device), None) if fused else (nn.BatchNorm2d(channels, device=device), nn.ReLU())
 
 
+def _feed_batch_norm(*convs):
+    """Mark convolutions whose output goes straight into a BatchNorm layer (see ``nn.Conv2d.feeds_batch_norm``)."""
+    for conv in convs:
+        conv.feeds_batch_norm = True
+
+
 class BasicBlock(nn.Module):
     """fused=True uses the fused BatchNorm+ReLU and add+ReLU operators (same arithmetic, fewer
-    passes over memory); fused=False composes the six reference layer types one by one."""
+    passes over memory); fused=False composes the six reference layer types one by one.
+    conv_stats=True lets every convolution reduce the batch statistics its BatchNorm needs."""
 
-    def __init__(self, cin, cout, stride, device="cpu", fused=True):
+    def __init__(self, cin, cout, stride, device="cpu", fused=True, conv_stats=True):
         super().__init__()
         self.fused = fused
         self.conv1 = nn.Conv2d(cin, cout, 3, stride, 1, bias=False, device=device)
@@ -42,6 +49,8 @@ class BasicBlock(nn.Module):
             self.downsample = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, 0, bias=False, device=device),
                                             nn.BatchNorm2d(cout, device=device))
         self.relu = nn.ReLU()
+        if conv_stats:
+            _feed_batch_norm(self.conv1, self.conv2, *([self.downsample._modules["0"]] if self.downsample is not None else []))
 
     def forward(self, x):
         y = self.bn1(self.conv1(x))
@@ -56,7 +65,7 @@ class ResNet18Cifar(nn.Module):
     """3x3 stride-1 stem without max-pool, stages of 2 BasicBlocks (strides 1/2/2/2), global
     average pool, Linear."""
 
-    def __init__(self, widths=(64, 128, 256, 512), num_classes=10, device="cpu", fused=True):
+    def __init__(self, widths=(64, 128, 256, 512), num_classes=10, device="cpu", fused=True, conv_stats=True):
         super().__init__()
         self.fused = fused
         self.conv1 = nn.Conv2d(3, widths[0], 3, 1, 1, bias=False, device=device)
@@ -66,10 +75,12 @@ class ResNet18Cifar(nn.Module):
         for si, wd in enumerate(widths):
             blocks = []
             for bi in range(2):
-                blocks.append(BasicBlock(cin, wd, 2 if (si > 0 and bi == 0) else 1, device=device, fused=fused))
+                blocks.append(BasicBlock(cin, wd, 2 if (si > 0 and bi == 0) else 1, device=device, fused=fused, conv_stats=conv_stats))
                 cin = wd
             setattr(self, f"layer{si + 1}", nn.Sequential(*blocks))
         self.fc = nn.Linear(cin, num_classes, device=device)
+        if conv_stats:
+            _feed_batch_norm(self.conv1)
 
     def forward(self, x):
         x = self.bn1(self.conv1(x))
@@ -96,6 +107,7 @@ class Bottleneck(nn.Module):
             self.downsample = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, 0, bias=False, device=device),
                                             nn.BatchNorm2d(cout, device=device))
         self.relu = nn.ReLU()
+        _feed_batch_norm(self.conv1, self.conv2, self.conv3, *([self.downsample._modules["0"]] if self.downsample is not None else []))
 
     def forward(self, x):
         y = self.relu(self.bn1(self.conv1(x)))
@@ -111,6 +123,7 @@ class ResNet50(nn.Module):
     def __init__(self, num_classes=1000, device="cpu"):
         super().__init__()
         self.conv1 = nn.Conv2d(3, 64, 7, 2, 3, bias=False, device=device)
+        _feed_batch_norm(self.conv1)
         self.bn1 = nn.BatchNorm2d(64, device=device)
         self.relu = nn.ReLU()
         self.maxpool = nn.MaxPool2d(3, 2, 1)

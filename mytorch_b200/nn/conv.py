@@ -24,6 +24,9 @@ class Conv2d(Module):
         self.register_parameter("weight", Parameter(mytorch.tensor(
             np.zeros((out_channels, in_channels, *self.kernel_size)), dtype=dtype, device=device)))
         self.register_parameter("bias", Parameter(mytorch.tensor(np.zeros((out_channels,)), dtype=dtype, device=device)) if bias else None)
+        # set by a model whose next layer is a BatchNorm: lets the CUDA convolution hand that layer its
+        # batch statistics (see nn.functional.conv2d); purely an optimisation, results are unchanged
+        self.feeds_batch_norm = False
         self.reset_parameters()
 
     def reset_parameters(self):
@@ -35,4 +38,4 @@ class Conv2d(Module):
                 self.bias.uniform_(-bound, bound)
 
     def forward(self, input):
-        return conv2d(input, self.weight, self.bias, self.stride, self.padding)
+        return conv2d(input, self.weight, self.bias, self.stride, self.padding, bn_stats=self.feeds_batch_norm and self.training)

@@ -3,7 +3,10 @@ from mytorch_b200.ops._common import dispatch, grad_enabled, record, tracker
 from mytorch_b200.tensor import MismatchDataTypesError, MismatchDevicesError, Tensor
 
 
-def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0) -> Tensor:
+def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0, bn_stats=False) -> Tensor:
+    """``bn_stats`` (no counterpart in the reference): the result goes straight into a BatchNorm layer
+    in training mode; the CUDA backend then lets the convolution reduce the batch statistics of its
+    own output, which BatchNorm picks up instead of re-reading the tensor.  Results are unchanged."""
     tensors = [input, weight] + ([bias] if bias is not None else [])
     if any(t.device != input.device for t in tensors):
         raise MismatchDevicesError([t.device for t in tensors])
@@ -11,7 +14,10 @@ def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0) -> Ten
         raise MismatchDataTypesError([t.dtype for t in tensors])
     stride = (stride, stride) if isinstance(stride, int) else tuple(stride)
     padding = (padding, padding) if isinstance(padding, int) else tuple(padding)
-    out = dispatch(input.device, "conv2d")(input, weight, bias, stride, padding)
+    if bn_stats and input.device.type == "cuda":
+        out = dispatch(input.device, "conv2d")(input, weight, bias, stride, padding, bn_stats=True)
+    else:
+        out = dispatch(input.device, "conv2d")(input, weight, bias, stride, padding)
     out.requires_grad = grad_enabled(input, weight, bias)
     return record("conv2d", [input, weight, bias, stride, padding], out)
 

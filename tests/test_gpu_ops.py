@@ -377,3 +377,48 @@ def test_bounded_wait_runs_out_reports_once_and_leaves_the_context_usable(g):
     assert env.tensor_core_status() == 0
     for a, b in zip(before, after):
         assert np.array_equal(a, b)
+
+
+@pytest.mark.parametrize("cfg", [
+    # n, cin, h, w, cout, k, s, p, bias        kernel the forward pass takes
+    (8, 64, 32, 32, 64, 3, 1, 1, None),      # row-staged, resident filter
+    (8, 64, 32, 32, 64, 3, 1, 1, 40.0),      # the same with a bias far larger than the spread of the outputs
+    (16, 128, 16, 16, 128, 3, 1, 1, None),   # row-staged, streamed filter
+    (3, 32, 17, 23, 96, 3, 1, 1, 1.0),       # row-staged, odd image, tiles straddling images
+    (16, 256, 8, 8, 256, 3, 1, 1, None),     # im2col kernel
+    (8, 64, 32, 32, 128, 3, 2, 1, None),     # im2col kernel, stride 2
+    (32, 512, 4, 4, 512, 3, 1, 1, None),     # im2col kernel, several column tiles per row tile
+    (8, 3, 32, 32, 64, 3, 1, 1, None),       # image stem (channels padded to one block)
+    (8, 64, 32, 32, 128, 1, 2, 0, None),     # 1x1 shortcut: too short a reduction, no statistics expected
+])
+def test_conv_epilogue_hands_batch_norm_its_statistics(g, cfg, monkeypatch):
+    """A convolution asked for BatchNorm statistics leaves partial (count, mean, M2) rows on its output;
+    BatchNorm forward from those rows matches the oracle's BatchNorm of that very output, and
+    BatchNorm's own statistics pass, to fp32 accuracy.  The convolution's output itself is bit-identical
+    with and without the statistics."""
+    n, ci, h, w, co, k, s, p, bias = cfg
+    if cfg[1] == 128:
+        monkeypatch.setenv("MTB_ROWCONV_MIN_ITEMS", "1")   # two position tiles per weight stage
+    rng = np.random.default_rng(abs(hash(cfg)) % (2 ** 31))
+    x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
+    wt = (rng.standard_normal((co, ci, k, k)) / np.sqrt(ci * k * k)).astype(np.float32)
+    b = None if bias is None else (bias + rng.standard_normal(co)).astype(np.float32)
+    gamma, beta = rng.uniform(0.5, 1.5, co).astype(np.float32), rng.standard_normal(co).astype(np.float32)
+    xt, wtt, bt = g.dev(x), g.dev(wt), (g.dev(b) if b is not None else None)
+    plain = g.op("conv2d")(xt, wtt, bt, (s, s), (p, p))
+    fused = g.op("conv2d")(xt, wtt, bt, (s, s), (p, p), bn_stats=True)
+    yh = g.host(fused)
+    assert np.array_equal(yh, g.host(plain))
+    expect_stats = k > 1
+    assert (getattr(fused, "_bn_partials", None) is not None) == expect_stats
+    outs = []
+    for src in (fused, plain):
+        rm, rv = g.dev(np.zeros(co, np.float32)), g.dev(np.ones(co, np.float32))
+        y, mean, var = g.op("batch_norm2d")(src, g.dev(gamma), g.dev(beta), 1e-5, True, 0.1, rm, rv)
+        outs.append([g.host(t) for t in (y, mean, var, rm, rv)])
+    ry, rmean, rvar, rrm, rrv = O.batch_norm2d_forward(yh, gamma, beta, 1e-5, True, 0.1, np.zeros(co, np.float32), np.ones(co, np.float32))
+    for got in outs:
+        assert rel_err(got[0], ry) < 2 * FP32_TOL
+        assert rel_err(got[1], rmean.reshape(-1)) < FP32_TOL and rel_err(got[2], rvar.reshape(-1)) < 2 * FP32_TOL
+        assert rel_err(got[3], rrm) < FP32_TOL and rel_err(got[4], rrv) < 2 * FP32_TOL
+    assert rel_err(outs[0][1], outs[1][1]) < FP32_TOL and rel_err(outs[0][2], outs[1][2]) < 2 * FP32_TOL
