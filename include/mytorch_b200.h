@@ -90,6 +90,19 @@ int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, con
 int mtb_batch_norm2d_forward_prestats_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps,
                                           double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var,
                                           int relu, const float* stats, int stats_rows, void* workspace, long long workspace_bytes, void* stream);
+/* y = max(0, batch_norm(x) + residual): BatchNorm, shortcut addition and ReLU of a residual block's tail in
+ * one normalise pass (the reference runs batch_norm2d, add_reference and relu_reference:
+ * mytorch/nn/batch_norm.py:123-135, mytorch/tensor.py:292-300, mytorch/nn/relu.py:5-10).  stats / stats_rows as
+ * in the prestats variant, or NULL / 0.  Backward recomputes the ReLU mask from x, the statistics and
+ * residual; dresidual receives the masked upstream gradient (the gradient of the added tensor). */
+int mtb_batch_norm2d_add_relu_forward_f32(int n, int c, int h, int w, const float* x, const float* residual, const float* gamma,
+                                          const float* beta, double eps, int training, double momentum, float* running_mean,
+                                          float* running_var, float* y, float* mean, float* var, const float* stats, int stats_rows,
+                                          void* workspace, long long workspace_bytes, void* stream);
+int mtb_batch_norm2d_add_relu_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
+                                           const float* residual, const float* gamma, const float* beta, double eps, float* dx,
+                                           float* dresidual, float* dgamma, float* dbeta, void* workspace, long long workspace_bytes,
+                                           void* stream);
 /* relu != 0 in forward fuses max(0, .) into the normalise pass; the same flag in backward masks dy where
  * gamma*xhat + beta < 0 (recomputed, so the ReLU output need not be kept).  beta may be NULL (= 0). */
 int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,

@@ -41,6 +41,8 @@ _SIGNATURES = {
     "mtb_batch_norm2d_workspace_bytes": ([_I, _I, _I, _I], _L),
     "mtb_batch_norm2d_forward_f32": ([_I, _I, _I, _I, _P, _P, _P, _D, _I, _D, _P, _P, _P, _P, _P, _I, _P, _L, _P], _I),
     "mtb_batch_norm2d_backward_f32": ([_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _D, _I, _P, _P, _P, _P, _L, _P], _I),
+    "mtb_batch_norm2d_add_relu_forward_f32": ([_I, _I, _I, _I, _P, _P, _P, _P, _D, _I, _D, _P, _P, _P, _P, _P, _P, _I, _P, _L, _P], _I),
+    "mtb_batch_norm2d_add_relu_backward_f32": ([_I, _I, _I, _I, _P, _P, _P, _P, _P, _P, _P, _D, _P, _P, _P, _P, _P, _L, _P], _I),
     "mtb_add_relu_f32": ([_P, _P, _P, _L, _P], _I),
     "mtb_add_relu_backward_f32": ([_P, _P, _P, _P, _L, _P], _I),
     "mtb_colsum_workspace_bytes": ([_I], _L),

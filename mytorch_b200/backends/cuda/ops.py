@@ -348,6 +348,41 @@ def cuda_batch_norm2d(x, weight, bias, eps, training, momentum, running_mean, ru
     return y, mean, var
 
 
+@_reg("cuda", "batch_norm2d_add_relu")
+def cuda_batch_norm2d_add_relu(x, residual, weight, bias, eps, training, momentum, running_mean, running_var):
+    """max(0, batch_norm2d(x) + residual) in one normalise pass; returns (y, mean, var)."""
+    _f32(x, residual, weight, bias, running_mean, running_var)
+    if x.shape != residual.shape:
+        from mytorch_b200.tensor import MismatchShapesError
+
+        raise MismatchShapesError([x.shape, residual.shape])
+    env = _env(x)
+    n, c, h, w = x.shape
+    y, mean, var = _new(x.shape, x), _new((c,), x), _new((c,), x)
+    ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
+    use_batch_stats = bool(training) or running_mean is None or running_var is None
+    pre = getattr(x, "_bn_partials", None) if use_batch_stats else None
+    env.lib.batch_norm2d_add_relu_forward_f32(n, c, h, w, _ptr(x), _ptr(residual), _ptr(weight), _ptr(bias), float(eps), int(use_batch_stats),
+                                              float(momentum), _ptr(running_mean), _ptr(running_var), _ptr(y), _ptr(mean), _ptr(var),
+                                              pre[0].ptr if pre else None, pre[1] if pre else 0, ws, ws_bytes, env.stream())
+    return y, mean, var
+
+
+@_reg("cuda", "batch_norm2d_add_relu_backward")
+def cuda_batch_norm2d_add_relu_backward(output_grad, mean, var, x, residual, weight, bias, eps):
+    """[dx, dresidual, dgamma, dbeta]"""
+    env = _env(x)
+    n, c, h, w = x.shape
+    dx, dres = _new(x.shape, x), _new(x.shape, x)
+    affine = weight is not None and bias is not None
+    dg = _grad_buffer(weight) if affine else None
+    db = _grad_buffer(bias) if affine else None
+    ws, ws_bytes = env.workspace(env.lib.batch_norm2d_workspace_bytes(n, c, h, w))
+    env.lib.batch_norm2d_add_relu_backward_f32(n, c, h, w, _ptr(output_grad), _ptr(mean), _ptr(var), _ptr(x), _ptr(residual), _ptr(weight), _ptr(bias),
+                                               float(eps), _ptr(dx), _ptr(dres), _ptr(dg), _ptr(db), ws, ws_bytes, env.stream())
+    return [dx, dres, dg, db]
+
+
 @_reg("cuda", "batch_norm2d_relu")
 def cuda_batch_norm2d_relu(x, weight, bias, eps, training, momentum, running_mean, running_var):
     """BatchNorm2d followed by ReLU in one normalise pass (the ReLU input is never stored)."""

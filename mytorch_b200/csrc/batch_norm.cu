@@ -5,6 +5,8 @@
 // finalise kernel, so results are bit-reproducible.
 #include "colreduce.cuh"
 
+MTB_API long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w);
+
 namespace {
 
 // ---------------------------------------------------------------- forward: statistics
@@ -157,10 +159,12 @@ __global__ void bn_eval_prep_kernel(int C, const float* __restrict__ gamma, floa
 
 // ---------------------------------------------------------------- forward: normalise
 
-template <int V, bool RELU>
+// MODE 0: y = bn(x); 1: y = max(0, bn(x)); 2: y = max(0, bn(x) + res) (res has the shape of x)
+template <int V, int MODE>
 __global__ void __launch_bounds__(256) bn_normalize_kernel(const float* __restrict__ x, float* __restrict__ y, long long rows, int C, int L,
                                                             long long rows_per_block, const float* __restrict__ mean,
-                                                            const float* __restrict__ scale, const float* __restrict__ beta) {
+                                                            const float* __restrict__ scale, const float* __restrict__ beta,
+                                                            const float* __restrict__ res) {
   const int lane = threadIdx.x & (L - 1);
   const int rsub = threadIdx.x / L;
   const int R = 256 / L;
@@ -179,10 +183,13 @@ __global__ void __launch_bounds__(256) bn_normalize_kernel(const float* __restri
   for (long long r = r0 + rsub; r < r1; r += R) {
     long long off = r * C + (long long)cg * V;
     VecF<V> f = vload<V>(x + off);
+    VecF<V> a;
+    if (MODE == 2) a = vload<V>(res + off);
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       float t = (f.v[i] - mu[i]) * g[i] + b[i];
-      f.v[i] = RELU ? fmaxf(t, 0.f) : t;
+      if (MODE == 2) t = t + a.v[i];
+      f.v[i] = MODE ? fmaxf(t, 0.f) : t;
     }
     vstore<V>(y + off, f);
   }
@@ -191,13 +198,14 @@ __global__ void __launch_bounds__(256) bn_normalize_kernel(const float* __restri
 // ---------------------------------------------------------------- backward
 
 // partial[p][0][c] = sum dy, partial[p][1][c] = sum dy * xhat over the CTA's rows.
-// RELU: the forward output went through max(0, .) in the same pass; the upstream gradient is
-// first masked where the (recomputed, bit-identical) normalised value is negative.
-template <int V, bool RELU>
+// MODE 1 / 2: the forward output went through max(0, .) (MODE 2: after adding `res`) in the same pass;
+// the upstream gradient is first masked where the (recomputed, bit-identical) value was negative.
+template <int V, int MODE>
 __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __restrict__ dy, const float* __restrict__ x, long long rows, int C, int L,
                                                               long long rows_per_block, const float* __restrict__ mean,
                                                               const float* __restrict__ var, float eps, const float* __restrict__ gamma,
-                                                              const float* __restrict__ beta, float* __restrict__ partial) {
+                                                              const float* __restrict__ beta, float* __restrict__ partial,
+                                                              const float* __restrict__ res) {
   const int lane = threadIdx.x & (L - 1);
   const int rsub = threadIdx.x / L;
   const int R = 256 / L;
@@ -220,10 +228,16 @@ __global__ void __launch_bounds__(256) bn_bwd_partial_kernel(const float* __rest
       long long off = r * C + (long long)cg * V;
       VecF<V> g = vload<V>(dy + off);
       VecF<V> f = vload<V>(x + off);
+      VecF<V> a;
+      if (MODE == 2) a = vload<V>(res + off);
 #pragma unroll
       for (int i = 0; i < V; ++i) {
         float gi = g.v[i];
-        if (RELU && (f.v[i] - mu[i]) * gs[i] + bt[i] < 0.f) gi = 0.f;
+        if (MODE) {
+          float t = (f.v[i] - mu[i]) * gs[i] + bt[i];
+          if (MODE == 2) t = t + a.v[i];
+          if (t < 0.f) gi = 0.f;
+        }
         a0[i] += gi;
         a1[i] += gi * ((f.v[i] - mu[i]) * rstd[i]);
       }
@@ -290,11 +304,12 @@ __global__ void __launch_bounds__(1024) bn_bwd_final_kernel(const float* __restr
   coef[2 * C + c] = rstd * dg * inv_m;  // k3: (x - mean) * k3 = xhat * dgamma / m
 }
 
-template <int V, bool RELU>
+// MODE 2 also writes the masked upstream gradient, which is the gradient of the added tensor, to dres.
+template <int V, int MODE>
 __global__ void __launch_bounds__(256) bn_bwd_dx_kernel(const float* __restrict__ dy, const float* __restrict__ x, float* __restrict__ dx,
                                                          long long rows, int C, int L, long long rows_per_block,
                                                          const float* __restrict__ mean, const float* __restrict__ coef,
-                                                         const float* __restrict__ beta) {
+                                                         const float* __restrict__ beta, const float* __restrict__ res, float* __restrict__ dres) {
   const int lane = threadIdx.x & (L - 1);
   const int rsub = threadIdx.x / L;
   const int R = 256 / L;
@@ -316,13 +331,21 @@ __global__ void __launch_bounds__(256) bn_bwd_dx_kernel(const float* __restrict_
     long long off = r * C + (long long)cg * V;
     VecF<V> g = vload<V>(dy + off);
     VecF<V> f = vload<V>(x + off);
+    VecF<V> a, m;
+    if (MODE == 2) a = vload<V>(res + off);
 #pragma unroll
     for (int i = 0; i < V; ++i) {
       float gi = g.v[i];
-      if (RELU && (f.v[i] - mu[i]) * k1[i] + bt[i] < 0.f) gi = 0.f;  // k1 = gamma / sigma, the forward's scale
+      if (MODE) {
+        float t = (f.v[i] - mu[i]) * k1[i] + bt[i];  // k1 = gamma / sigma, the forward's scale
+        if (MODE == 2) t = t + a.v[i];
+        if (t < 0.f) gi = 0.f;
+      }
+      m.v[i] = gi;
       g.v[i] = k1[i] * (gi - k2[i] - (f.v[i] - mu[i]) * k3[i]);
     }
     vstore<V>(dx + off, g);
+    if (MODE == 2) vstore<V>(dres + off, m);
   }
 }
 
@@ -343,17 +366,81 @@ ColCfg stream_cfg(long long rows, int C, bool aligned) {
 }
 
 int launch_normalize(const float* x, float* y, long long rows, int c, bool aligned, const float* mean, const float* scale, const float* beta,
-                     int relu, cudaStream_t st) {
+                     int mode, const float* res, cudaStream_t st) {
   ColCfg s = stream_cfg(rows, c, aligned);
   dim3 grid(s.col_blocks, s.row_blocks);
-  if (s.vec == 4) {
-    if (relu) bn_normalize_kernel<4, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-    else bn_normalize_kernel<4, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-  } else {
-    if (relu) bn_normalize_kernel<1, true><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-    else bn_normalize_kernel<1, false><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta);
-  }
+#define MTB_BN_NORM(V_, M_) bn_normalize_kernel<V_, M_><<<grid, 256, 0, st>>>(x, y, rows, c, s.lanes, s.rows_per_block, mean, scale, beta, res)
+  if (s.vec == 4) { if (mode == 2) MTB_BN_NORM(4, 2); else if (mode == 1) MTB_BN_NORM(4, 1); else MTB_BN_NORM(4, 0); }
+  else { if (mode == 2) MTB_BN_NORM(1, 2); else if (mode == 1) MTB_BN_NORM(1, 1); else MTB_BN_NORM(1, 0); }
+#undef MTB_BN_NORM
   MTB_LAUNCH_CHECK("bn_normalize_kernel");
+  return MTB_OK;
+}
+
+// mode 0: y = bn(x); 1: y = max(0, bn(x)); 2: y = max(0, bn(x) + res).  stats / stats_rows: batch statistics
+// prepared by the producer of x as partial rows (see mtb_conv2d_forward_stats_f32); 0 rows = compute them here.
+int bn_forward(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps, int training, double momentum,
+               float* running_mean, float* running_var, float* y, float* mean, float* var, int mode, const float* res, const float* stats,
+               int stats_rows, void* workspace, long long workspace_bytes, cudaStream_t st) {
+  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && x && y && mean && var && workspace, "batch_norm2d_forward: bad arguments");
+  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_forward: workspace too small");
+  MTB_REQUIRE(training || (running_mean && running_var), "batch_norm2d_forward: inference needs running statistics");
+  MTB_REQUIRE(mode != 2 || res, "batch_norm2d_add_relu_forward: the tensor to add is missing");
+  long long rows = (long long)n * h * w;
+  bool aligned = mtb_aligned16(x) && mtb_aligned16(y) && (mode != 2 || mtb_aligned16(res));
+  float* partial = (float*)workspace;
+  float* scale = partial + (long long)mtb_col_max_partials() * 3 * c;
+  if (training) {
+    int P = stats_rows;
+    if (!(stats && stats_rows > 0)) {
+      ColCfg cfg = mtb_col_cfg(rows, c, mtb_aligned16(x));
+      dim3 grid(cfg.col_blocks, cfg.row_blocks);
+      if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+      else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
+      MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
+      stats = partial;
+      P = cfg.row_blocks;
+    }
+    bn_stats_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(stats, P, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
+                                                              running_mean, running_var, mean, var, scale);
+    MTB_LAUNCH_CHECK("bn_stats_final_kernel");
+  } else {
+    bn_eval_prep_kernel<<<mtb_div_up(c, 128), 128, 0, st>>>(c, gamma, (float)eps, running_mean, running_var, mean, var, scale);
+    MTB_LAUNCH_CHECK("bn_eval_prep_kernel");
+  }
+  return launch_normalize(x, y, rows, c, aligned, mean, scale, beta, mode, res, st);
+}
+
+// dx = gamma/sigma * (g - dbeta/m - xhat * dgamma/m) with g = dy masked by the forward's ReLU (modes 1, 2);
+// mode 2 also writes g to dres (the gradient of the added tensor).
+int bn_backward(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x, const float* gamma,
+                const float* beta, double eps, int mode, const float* res, float* dx, float* dres, float* dgamma, float* dbeta, void* workspace,
+                long long workspace_bytes, cudaStream_t st) {
+  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && dy && mean && var && x && dx && workspace, "batch_norm2d_backward: bad arguments");
+  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_backward: workspace too small");
+  MTB_REQUIRE(mode != 2 || (res && dres), "batch_norm2d_add_relu_backward: the added tensor and its gradient buffer are required");
+  long long rows = (long long)n * h * w;
+  bool aligned = mtb_aligned16(x) && mtb_aligned16(dy) && mtb_aligned16(dx) && (mode != 2 || (mtb_aligned16(res) && mtb_aligned16(dres)));
+  float* partial = (float*)workspace;
+  float* coef = partial + (long long)mtb_col_max_partials() * 3 * c;  // 3*C floats fit in the 4*C tail
+  ColCfg cfg = mtb_col_cfg(rows, c, aligned);
+  dim3 grid(cfg.col_blocks, cfg.row_blocks);
+#define MTB_BN_PARTIAL(V_, M_) \
+  bn_bwd_partial_kernel<V_, M_><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, gamma, beta, partial, res)
+  if (cfg.vec == 4) { if (mode == 2) MTB_BN_PARTIAL(4, 2); else if (mode == 1) MTB_BN_PARTIAL(4, 1); else MTB_BN_PARTIAL(4, 0); }
+  else { if (mode == 2) MTB_BN_PARTIAL(1, 2); else if (mode == 1) MTB_BN_PARTIAL(1, 1); else MTB_BN_PARTIAL(1, 0); }
+#undef MTB_BN_PARTIAL
+  MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
+  bn_bwd_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
+                                                          dgamma, dbeta, coef);
+  MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
+  ColCfg s = stream_cfg(rows, c, aligned);
+  dim3 g2(s.col_blocks, s.row_blocks);
+#define MTB_BN_DX(V_, M_) bn_bwd_dx_kernel<V_, M_><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef, beta, res, dres)
+  if (s.vec == 4) { if (mode == 2) MTB_BN_DX(4, 2); else if (mode == 1) MTB_BN_DX(4, 1); else MTB_BN_DX(4, 0); }
+  else { if (mode == 2) MTB_BN_DX(1, 2); else if (mode == 1) MTB_BN_DX(1, 1); else MTB_BN_DX(1, 0); }
+#undef MTB_BN_DX
+  MTB_LAUNCH_CHECK("bn_bwd_dx_kernel");
   return MTB_OK;
 }
 
@@ -372,29 +459,8 @@ MTB_API long long mtb_batch_norm2d_workspace_bytes(int n, int c, int h, int w) {
 MTB_API int mtb_batch_norm2d_forward_f32(int n, int c, int h, int w, const float* x, const float* gamma, const float* beta, double eps,
                                          int training, double momentum, float* running_mean, float* running_var, float* y,
                                          float* mean, float* var, int relu, void* workspace, long long workspace_bytes, void* stream) {
-  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && x && y && mean && var && workspace, "batch_norm2d_forward: bad arguments");
-  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_forward: workspace too small");
-  MTB_REQUIRE(training || (running_mean && running_var), "batch_norm2d_forward: inference needs running statistics");
-  cudaStream_t st = (cudaStream_t)stream;
-  long long rows = (long long)n * h * w;
-  bool aligned = mtb_aligned16(x) && mtb_aligned16(y);
-  float* partial = (float*)workspace;
-  float* scale = partial + (long long)mtb_col_max_partials() * 3 * c;
-  int fin_blocks = mtb_div_up(c, 128);
-  if (training) {
-    ColCfg cfg = mtb_col_cfg(rows, c, aligned);
-    dim3 grid(cfg.col_blocks, cfg.row_blocks);
-    if (cfg.vec == 4) bn_stats_partial_kernel<4><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
-    else bn_stats_partial_kernel<1><<<grid, 256, 0, st>>>(x, rows, c, cfg.lanes, cfg.rows_per_block, partial);
-    MTB_LAUNCH_CHECK("bn_stats_partial_kernel");
-    bn_stats_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
-                                                      running_mean, running_var, mean, var, scale);
-    MTB_LAUNCH_CHECK("bn_stats_final_kernel");
-  } else {
-    bn_eval_prep_kernel<<<fin_blocks, 128, 0, st>>>(c, gamma, (float)eps, running_mean, running_var, mean, var, scale);
-    MTB_LAUNCH_CHECK("bn_eval_prep_kernel");
-  }
-  return launch_normalize(x, y, rows, c, aligned, mean, scale, beta, relu, st);
+  return bn_forward(n, c, h, w, x, gamma, beta, eps, training, momentum, running_mean, running_var, y, mean, var, relu ? 1 : 0, nullptr, nullptr, 0,
+                    workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 // Training-mode forward whose batch statistics were prepared by the producer of x: `stats` holds
@@ -405,16 +471,20 @@ MTB_API int mtb_batch_norm2d_forward_prestats_f32(int n, int c, int h, int w, co
                                                   double momentum, float* running_mean, float* running_var, float* y, float* mean, float* var,
                                                   int relu, const float* stats, int stats_rows, void* workspace, long long workspace_bytes,
                                                   void* stream) {
-  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && x && y && mean && var && workspace && stats && stats_rows > 0,
-              "batch_norm2d_forward_prestats: bad arguments");
-  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_forward_prestats: workspace too small");
-  cudaStream_t st = (cudaStream_t)stream;
-  const long long rows = (long long)n * h * w;
-  float* scale = (float*)workspace + (long long)mtb_col_max_partials() * 3 * c;
-  bn_stats_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(stats, stats_rows, c, gamma, (float)eps, (float)(1.0 - momentum), (float)momentum,
-                                                            running_mean, running_var, mean, var, scale);
-  MTB_LAUNCH_CHECK("bn_stats_final_kernel");
-  return launch_normalize(x, y, rows, c, mtb_aligned16(x) && mtb_aligned16(y), mean, scale, beta, relu, st);
+  MTB_REQUIRE(stats && stats_rows > 0, "batch_norm2d_forward_prestats: no statistics rows");
+  return bn_forward(n, c, h, w, x, gamma, beta, eps, 1, momentum, running_mean, running_var, y, mean, var, relu ? 1 : 0, nullptr, stats, stats_rows,
+                    workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+// y = max(0, batch_norm(x) + residual): the tail of a residual block (BatchNorm, shortcut addition, ReLU) in
+// one normalise pass; the BatchNorm output is never stored.  stats / stats_rows as above (NULL / 0: the
+// statistics are computed here).  residual has the shape of x.
+MTB_API int mtb_batch_norm2d_add_relu_forward_f32(int n, int c, int h, int w, const float* x, const float* residual, const float* gamma,
+                                                  const float* beta, double eps, int training, double momentum, float* running_mean,
+                                                  float* running_var, float* y, float* mean, float* var, const float* stats, int stats_rows,
+                                                  void* workspace, long long workspace_bytes, void* stream) {
+  return bn_forward(n, c, h, w, x, gamma, beta, eps, training, momentum, running_mean, running_var, y, mean, var, 2, residual, stats, stats_rows,
+                    workspace, workspace_bytes, (cudaStream_t)stream);
 }
 
 // dx = gamma/sigma * (dy - dbeta/m - xhat * dgamma/m); dgamma, dbeta may be NULL (not affine).
@@ -423,30 +493,17 @@ MTB_API int mtb_batch_norm2d_forward_prestats_f32(int n, int c, int h, int w, co
 MTB_API int mtb_batch_norm2d_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var, const float* x,
                                           const float* gamma, const float* beta, double eps, int relu, float* dx, float* dgamma,
                                           float* dbeta, void* workspace, long long workspace_bytes, void* stream) {
-  MTB_REQUIRE(n > 0 && c > 0 && h > 0 && w > 0 && dy && mean && var && x && dx && workspace, "batch_norm2d_backward: bad arguments");
-  MTB_REQUIRE(workspace_bytes >= mtb_batch_norm2d_workspace_bytes(n, c, h, w), "batch_norm2d_backward: workspace too small");
-  cudaStream_t st = (cudaStream_t)stream;
-  long long rows = (long long)n * h * w;
-  bool aligned = mtb_aligned16(x) && mtb_aligned16(dy) && mtb_aligned16(dx);
-  float* partial = (float*)workspace;
-  float* coef = partial + (long long)mtb_col_max_partials() * 3 * c;  // 3*C floats fit in the 4*C tail
-  ColCfg cfg = mtb_col_cfg(rows, c, aligned);
-  dim3 grid(cfg.col_blocks, cfg.row_blocks);
-#define MTB_BN_PARTIAL(V_, R_) \
-  bn_bwd_partial_kernel<V_, R_><<<grid, 256, 0, st>>>(dy, x, rows, c, cfg.lanes, cfg.rows_per_block, mean, var, (float)eps, gamma, beta, partial)
-  if (cfg.vec == 4) { if (relu) MTB_BN_PARTIAL(4, true); else MTB_BN_PARTIAL(4, false); }
-  else { if (relu) MTB_BN_PARTIAL(1, true); else MTB_BN_PARTIAL(1, false); }
-#undef MTB_BN_PARTIAL
-  MTB_LAUNCH_CHECK("bn_bwd_partial_kernel");
-  bn_bwd_final_kernel<<<mtb_div_up(c, 8), 1024, 0, st>>>(partial, cfg.row_blocks, c, gamma, var, (float)eps, (float)(1.0 / (double)rows),
-                                                          dgamma, dbeta, coef);
-  MTB_LAUNCH_CHECK("bn_bwd_final_kernel");
-  ColCfg s = stream_cfg(rows, c, aligned);
-  dim3 g2(s.col_blocks, s.row_blocks);
-#define MTB_BN_DX(V_, R_) bn_bwd_dx_kernel<V_, R_><<<g2, 256, 0, st>>>(dy, x, dx, rows, c, s.lanes, s.rows_per_block, mean, coef, beta)
-  if (s.vec == 4) { if (relu) MTB_BN_DX(4, true); else MTB_BN_DX(4, false); }
-  else { if (relu) MTB_BN_DX(1, true); else MTB_BN_DX(1, false); }
-#undef MTB_BN_DX
-  MTB_LAUNCH_CHECK("bn_bwd_dx_kernel");
-  return MTB_OK;
+  return bn_backward(n, c, h, w, dy, mean, var, x, gamma, beta, eps, relu ? 1 : 0, nullptr, dx, nullptr, dgamma, dbeta, workspace, workspace_bytes,
+                     (cudaStream_t)stream);
+}
+
+// Backward of mtb_batch_norm2d_add_relu_forward_f32: the ReLU mask is recomputed from x, the statistics and
+// residual with the forward's own expression; dresidual receives the masked upstream gradient (the
+// gradient of the added tensor), dx the BatchNorm input gradient.
+MTB_API int mtb_batch_norm2d_add_relu_backward_f32(int n, int c, int h, int w, const float* dy, const float* mean, const float* var,
+                                                   const float* x, const float* residual, const float* gamma, const float* beta, double eps,
+                                                   float* dx, float* dresidual, float* dgamma, float* dbeta, void* workspace,
+                                                   long long workspace_bytes, void* stream) {
+  return bn_backward(n, c, h, w, dy, mean, var, x, gamma, beta, eps, 2, residual, dx, dresidual, dgamma, dbeta, workspace, workspace_bytes,
+                     (cudaStream_t)stream);
 }

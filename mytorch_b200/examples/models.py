@@ -33,8 +33,8 @@ def _feed_batch_norm(*convs):
 
 
 class BasicBlock(nn.Module):
-    """fused=True uses the fused BatchNorm+ReLU and add+ReLU operators (same arithmetic, fewer
-    passes over memory); fused=False composes the six reference layer types one by one.
+    """fused=True uses the fused BatchNorm+ReLU and BatchNorm+add+ReLU operators (same arithmetic,
+    fewer passes over memory); fused=False composes the six reference layer types one by one.
     conv_stats=True lets every convolution reduce the batch statistics its BatchNorm needs."""
 
     def __init__(self, cin, cout, stride, device="cpu", fused=True, conv_stats=True):
@@ -43,7 +43,7 @@ class BasicBlock(nn.Module):
         self.conv1 = nn.Conv2d(cin, cout, 3, stride, 1, bias=False, device=device)
         self.bn1 = nn.BatchNormReLU2d(cout, device=device) if fused else nn.BatchNorm2d(cout, device=device)
         self.conv2 = nn.Conv2d(cout, cout, 3, 1, 1, bias=False, device=device)
-        self.bn2 = nn.BatchNorm2d(cout, device=device)
+        self.bn2 = nn.BatchNormAddReLU2d(cout, device=device) if fused else nn.BatchNorm2d(cout, device=device)
         self.downsample = None
         if stride != 1 or cin != cout:
             self.downsample = nn.Sequential(nn.Conv2d(cin, cout, 1, stride, 0, bias=False, device=device),
@@ -56,9 +56,10 @@ class BasicBlock(nn.Module):
         y = self.bn1(self.conv1(x))
         if not self.fused:
             y = self.relu(y)
-        y = self.bn2(self.conv2(y))
         shortcut = x if self.downsample is None else self.downsample(x)
-        return F.add_relu(y, shortcut) if self.fused else self.relu(y + shortcut)
+        if self.fused:
+            return self.bn2(self.conv2(y), shortcut)
+        return self.relu(self.bn2(self.conv2(y)) + shortcut)
 
 
 class ResNet18Cifar(nn.Module):

@@ -2,7 +2,7 @@
 running var 1; training mode normalises with batch statistics and blends the *biased* batch
 variance into ``running_var``."""
 from mytorch_b200.dtype import float32
-from mytorch_b200.nn.functional.batch_norm import _batch_norm2d, _batch_norm2d_relu
+from mytorch_b200.nn.functional.batch_norm import _batch_norm2d, _batch_norm2d_add_relu, _batch_norm2d_relu
 from mytorch_b200.nn.module import Module
 from mytorch_b200.nn.parameter import Parameter
 from mytorch_b200.tensor import Tensor
@@ -45,3 +45,12 @@ class BatchNormReLU2d(BatchNorm2d):
 
     def forward(self, x):
         return _batch_norm2d_relu(x, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean, self.running_var)
+
+
+class BatchNormAddReLU2d(BatchNorm2d):
+    """The tail of a residual block as one fused operator: ``forward(x, residual)`` returns
+    ``ReLU()(BatchNorm2d(...)(x) + residual)``.  Same parameters, buffers and state-dict keys as ``BatchNorm2d``."""
+
+    def forward(self, x, residual):
+        return _batch_norm2d_add_relu(x, residual, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean,
+                                      self.running_var)

@@ -358,9 +358,46 @@ def dp_cases():
     np.savez_compressed(os.path.join(OUT, "data_parallel.npz"), **out)
 
 
+def checkpoint_case():
+    """A checkpoint written by the reference's own ``mytorch.save`` after one SGD-momentum step of a small
+    Conv-BN-ReLU-MaxPool-Linear net (model and optimizer state dicts), and what the reference computes
+    when it takes the next step from that state: the file must load into the new implementation and
+    the continued step must agree."""
+    import mytorch
+
+    class Flat(nn.Module):
+        def forward(self, x):
+            return x.reshape((x.shape[0], -1))
+
+    rng = np.random.default_rng(3003)
+    x = rng.standard_normal((8, 3, 12, 12)).astype(f32)
+    t = rng.integers(0, 5, 8).astype(np.int64)
+    manual_seed(3003)
+    net = nn.Sequential(nn.Conv2d(3, 8, 3, 1, 1), nn.BatchNorm2d(8), nn.ReLU(), nn.MaxPool2d(2, 2), Flat(), nn.Linear(8 * 6 * 6, 5))
+    opt = SGD(net.parameters(), lr=0.05, momentum=0.9)
+
+    def step():
+        loss = F.cross_entropy(net(T(x)), T(t))
+        opt.zero_grad()
+        loss.backward()
+        opt.step()
+        return loss.item()
+
+    out = {"loss0": np.array(step())}
+    mytorch.save({"model": net.state_dict(), "optimizer": opt.state_dict()}, os.path.join(OUT, "reference_checkpoint.pt"))
+    for k, v in net.state_dict().items():
+        out[f"saved/{k}"] = npy(v).copy()
+    for i, p in enumerate(net.parameters()):
+        out[f"momentum/{i}"] = npy(opt.state[p]["momentum_buffer"]).copy()
+    out["loss1"] = np.array(step())
+    for k, v in net.state_dict().items():
+        out[f"next/{k}"] = npy(v).copy()
+    np.savez_compressed(os.path.join(OUT, "checkpoint.npz"), **out)
+
+
 if __name__ == "__main__":
     only = sys.argv[2:]  # optional: names of the fixture groups to regenerate
-    groups = {"conv": conv_cases, "bn": bn_cases, "pool": pool_cases, "misc": misc_cases, "models": model_cases, "dp": dp_cases}
+    groups = {"conv": conv_cases, "bn": bn_cases, "pool": pool_cases, "misc": misc_cases, "models": model_cases, "dp": dp_cases, "checkpoint": checkpoint_case}
     for name, fn in groups.items():
         if not only or name in only:
             fn()

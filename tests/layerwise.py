@@ -62,6 +62,14 @@ class LayerwiseChecker:
             self._note("fwd", name, y, ry, FP32_TOL)
             self._note("fwd", name + ".mean", _h(helpers[0]), mean.reshape(-1), FP32_TOL)
             self._note("fwd", name + ".var", _h(helpers[1]), var.reshape(-1), FP32_TOL)
+        elif name == "batch_norm2d_add_relu":
+            x, res, g, b, eps = inputs
+            ry, mean, var, _, _ = O.batch_norm2d_forward(_h(x.detach()), _h(g.detach()), _h(b.detach()), eps, True, 0.1, None, None)
+            ry = O.relu_forward(O.add_forward(ry, _h(res.detach()), 1))
+            self._fused_out[id(x)] = y
+            self._note("fwd", name, y, ry, FP32_TOL)
+            self._note("fwd", name + ".mean", _h(helpers[0]), mean.reshape(-1), FP32_TOL)
+            self._note("fwd", name + ".var", _h(helpers[1]), var.reshape(-1), FP32_TOL)
         elif name == "relu":
             assert np.array_equal(y, O.relu_forward(_h(inputs[0].detach())))
         elif name == "max_pool2d":
@@ -119,6 +127,22 @@ class LayerwiseChecker:
                 self._note("bwd", name + ".dx", g[0], rdx, FP32_TOL * 2)
                 self._note("bwd", name + ".dgamma", g[1], rdg, FP32_TOL * 3)
                 self._note("bwd", name + ".dbeta", g[2], rdb, FP32_TOL * 3)
+            elif name == "batch_norm2d_add_relu":
+                dy, mean, var, x, res, gam, b, eps = args
+                c = x.shape[1]
+                hm, hv, hx, hdy = _h(mean).reshape(1, c, 1, 1), _h(var).reshape(1, c, 1, 1), _h(x.detach()), _h(dy)
+                # the reference would run relu_backward on (BatchNorm output + residual): the gradient is
+                # blocked only where that sum is negative; taken from the recorded output (y > 0) plus the
+                # elements whose sum is exactly zero
+                hg, hb = _h(gam.detach()).reshape(1, c, 1, 1), _h(b.detach()).reshape(1, c, 1, 1)
+                pre = (hx - hm) * (hg / np.sqrt(hv + np.float32(eps), dtype=np.float32)) + hb + _h(res.detach())
+                keep = (self._fused_out[id(x)] > 0) | (pre == 0)
+                masked = np.where(keep, hdy, 0).astype(hdy.dtype)
+                assert np.array_equal(g[1], masked)   # gradient of the added tensor
+                rdx, rdg, rdb = O.batch_norm2d_backward(masked, hm, hv, hx, _h(gam.detach()), eps)
+                self._note("bwd", name + ".dx", g[0], rdx, FP32_TOL * 2)
+                self._note("bwd", name + ".dgamma", g[2], rdg, FP32_TOL * 3)
+                self._note("bwd", name + ".dbeta", g[3], rdb, FP32_TOL * 3)
             elif name == "relu":
                 assert np.array_equal(g[0], O.relu_backward(_h(args[0]), _h(args[1].detach())))
             elif name == "add_relu":
