@@ -145,7 +145,7 @@ int mtb_binary_strided_f32(int op, int ndim, const long long* shape, const long 
 int mtb_resize_channels_f32(const float* src, float* dst, long long rows, int c_src, int c_dst, void* stream);
 int mtb_nchw_to_nhwc_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
 int mtb_nhwc_to_nchw_f32(const float* src, float* dst, int n, int c, int h, int w, void* stream);
-/* kind: 0 int32->int64, 1 int64->float32, 2 float32->int64 (replaces cast_reference, cast.cu/source.cu:5-14) */
+/* kind: 0 int32->int64, 1 int64->float32, 2 float32->int64, 3 int8->float32 (replaces cast_reference, cast.cu/source.cu:5-14) */
 int mtb_cast(int kind, const void* src, void* dst, long long n, void* stream);
 
 /* ---- reductions (replace sum_scale_reference / _backward, mytorch/native/cuda/reduce_ops.cu/1.template, 2.template,
@@ -165,6 +165,16 @@ int mtb_nhwc_spatial_sum_f32(const float* x, float* y, int n, int c, int hw, flo
 int mtb_nhwc_spatial_bcast_f32(const float* dy, float* dx, int n, int c, int hw, float scale, void* stream);
 int mtb_sum_strided_f32(const float* x, float* y, int nkept, const long long* kept_shape, const long long* kept_strides, int nred,
                         const long long* red_shape, const long long* red_strides, float scale, void* stream);
+
+/* ---- max with indices, equality (replace MaxReference_<dt> / max_backward_reference_<dt>, mytorch/backends/cuda/ops/max.py:10-120,
+ *      and the eq kernel, mytorch/backends/cuda/ops/eq.py:9).  Shapes and strides are HOST arrays, strides in elements. ---- */
+int mtb_max_strided_f32(const float* x, float* y, long long* idx, int nkept, const long long* kept_shape, const long long* kept_strides,
+                        long long red_len, long long red_stride, void* stream);
+int mtb_max_backward_f32(const float* dy, const long long* idx, float* dx, long long dx_elems, int nkept, const long long* kept_shape,
+                         const long long* kept_strides, long long red_stride, void* stream);
+/* out: int8, dense in logical order; kind 0 float32, 1 int64 */
+int mtb_eq_strided(int kind, int ndim, const long long* shape, const long long* x_strides, const long long* y_strides, const void* x,
+                   const void* y, signed char* out, void* stream);
 
 /* ---- softmax cross-entropy (replaces cross_entropy_reference / _backward_reference,
  *      mytorch/native/cuda/cross_entropy.cu/source.cu:6-99); target is int64 ---- */

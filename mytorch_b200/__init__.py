@@ -9,11 +9,13 @@ from .autograd import no_grad
 from .dtype import (DType, float16, float32, float64, int8, int16, int32, int64, uint8, uint16, uint32, uint64)
 from .rand_generator import manual_seed
 from .tensor import Device, Tensor, tensor
-from .ops.basic_ops import mm, permute, reshape
+from .ops.basic_ops import bmm, mm, permute, reshape
+from .ops.eq import eq
+from .ops.max import max
 from .ops.broadcast_binary_ops import add, div, mul, pow, sub
 from .ops.reduce_ops import mean, sum
 from .serialization import load, save
 
-__all__ = ["Tensor", "tensor", "Device", "no_grad", "manual_seed", "mm", "permute", "reshape", "add", "sub", "mul", "div", "pow",
+__all__ = ["Tensor", "tensor", "Device", "no_grad", "manual_seed", "mm", "bmm", "permute", "reshape", "max", "eq", "add", "sub", "mul", "div", "pow",
            "sum", "mean", "save", "load", "DType", "float16", "float32", "float64", "int8", "int16", "int32", "int64", "uint8",
            "uint16", "uint32", "uint64"]

@@ -51,6 +51,9 @@ _SIGNATURES = {
     "mtb_nhwc_spatial_sum_f32": ([_P, _P, _I, _I, _I, _F, _P], _I),
     "mtb_nhwc_spatial_bcast_f32": ([_P, _P, _I, _I, _I, _F, _P], _I),
     "mtb_sum_strided_f32": ([_P, _P, _I, _P, _P, _I, _P, _P, _F, _P], _I),
+    "mtb_max_strided_f32": ([_P, _P, _P, _I, _P, _P, _L, _L, _P], _I),
+    "mtb_max_backward_f32": ([_P, _P, _P, _L, _I, _P, _P, _L, _P], _I),
+    "mtb_eq_strided": ([_I, _I, _P, _P, _P, _P, _P, _P, _P], _I),
     "mtb_max_pool2d_forward_f32": (_POOL + [_P, _P, _P, _P], _I),
     "mtb_max_pool2d_backward_f32": (_POOL + [_P, _P, _P, _P, _P, _P], _I),
     "mtb_max_pool2d_argmax_u8": ([_P, _P, _L, _P], _I),

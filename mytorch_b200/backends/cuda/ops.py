@@ -542,7 +542,9 @@ def cuda_copy(dst, src):
 @_reg("cuda", "cast")
 def cuda_cast(x, dtype):
     env = _env(x)
-    kinds = {(int32, int64): 0, (int64, float32): 1, (float32, int64): 2}
+    from mytorch_b200.dtype import int8
+
+    kinds = {(int32, int64): 0, (int64, float32): 1, (float32, int64): 2, (int8, float32): 3}
     kind = kinds.get((x.dtype, dtype))
     if kind is None:
         raise RuntimeError(f"cast from {x.dtype} to {dtype} is not available on the cuda backend")
@@ -555,7 +557,7 @@ def cuda_cast(x, dtype):
 
 # ---------------------------------------------------------------------------- broadcast binary ops
 
-_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4}
+_OPS = {"add": 0, "sub": 1, "mul": 2, "div": 3, "pow": 4, "pow_dx": 6, "pow_dy": 7}
 
 
 def _bstrides(t, out_shape):
@@ -644,6 +646,125 @@ def cuda_sub_backward(output_grad, x, y, alpha):
 @_reg("cuda", "mul_backward")
 def cuda_mul_backward(output_grad, x, y):
     return _reduce_to(_binary("mul", output_grad, y), x.shape, x), _reduce_to(_binary("mul", output_grad, x), y.shape, y)
+
+
+@_reg("cuda", "div_backward")
+def cuda_div_backward(output_grad, x, y):
+    """dx = dy / y, dy_ = -x / y^2 * dy (``mytorch/backends/cpu/ops/broadcast_binary_ops.py:108-115``)."""
+    gx = _binary("div", output_grad, y)
+    gy = _scaled(_binary("div", _binary("mul", output_grad, x), _binary("mul", y, y)), -1.0)
+    return _reduce_to(gx, x.shape, x), _reduce_to(gy, y.shape, y)
+
+
+@_reg("cuda", "pow_backward")
+def cuda_pow_backward(output_grad, x, y):
+    """dx = y x^(y-1) dy, dy_ = x^y ln(x) dy (``mytorch/backends/cpu/ops/broadcast_binary_ops.py:130-137``)."""
+    gx = _binary("mul", _binary("pow_dx", x, y), output_grad)
+    gy = _binary("mul", _binary("pow_dy", x, y), output_grad)
+    return _reduce_to(gx, x.shape, x), _reduce_to(gy, y.shape, y)
+
+
+# ---------------------------------------------------------------------------- max / eq / bmm
+
+@_reg("cuda", "max")
+def cuda_max(tensor, dim, keepdim):
+    """(values, int64 indices) of the maximum along ``dim`` (``None``: over everything, index into the
+    flattened logical tensor); ties go to the first element (``mytorch/backends/cuda/ops/max.py:10-75``)."""
+    _f32(tensor)
+    if dim is not None and not isinstance(dim, int):
+        raise RuntimeError(f"max dimension must be a integer or None: {dim}")
+    env = _env(tensor)
+    nd = len(tensor.shape)
+    src = tensor
+    if dim is None:
+        if _nontrivial_nhwc(tensor):  # flat indices refer to the logical order
+            src = cuda_reshape(tensor, (_numel(tensor.shape),))
+        kept_shape, kept_strides, red_len, red_stride = [], [], _numel(tensor.shape), 1
+        out_shape = calculate_reduce_shape(tensor.shape, tuple(range(nd)), keepdim)
+    else:
+        dim = dim + nd if dim < 0 else dim
+        st = _strides(tensor)
+        kept = [i for i in range(nd) if i != dim]
+        kept_shape, kept_strides = [tensor.shape[i] for i in kept], [st[i] for i in kept]
+        red_len, red_stride = tensor.shape[dim], st[dim]
+        out_shape = calculate_reduce_shape(tensor.shape, (dim,), keepdim)
+    n_out = _numel(out_shape)
+    values = _T()(shape=(n_out,), dtype=tensor.dtype, device=tensor.device)
+    indices = _T()(shape=tuple(out_shape), dtype=int64, device=tensor.device)
+    env.lib.max_strided_f32(_ptr(src), _ptr(values), _ptr(indices), len(kept_shape), _ll(kept_shape), _ll(kept_strides), red_len, red_stride,
+                            env.stream())
+    return cuda_reshape(values, tuple(out_shape)), indices
+
+
+@_reg("cuda", "max_backward")
+def cuda_max_backward(output_grad, indices_tensor, tensor, dim, keepdim):
+    env = _env(tensor)
+    nd = len(tensor.shape)
+    dx = _new(tensor.shape, tensor)
+    g = output_grad
+    if _nontrivial_nhwc(g):  # the kernel reads dy in logical (dense) order, like the indices
+        g = cuda_reshape(g, (_numel(g.shape),))
+    if dim is None:
+        flat = _T()(shape=(_numel(tensor.shape),), dtype=tensor.dtype, device=tensor.device)
+        env.lib.max_backward_f32(_ptr(g), _ptr(indices_tensor), _ptr(flat), _numel(tensor.shape), 0, _ll([]), _ll([]), 1, env.stream())
+        return [cuda_reshape(flat, tensor.shape)]
+    dim = dim + nd if dim < 0 else dim
+    st = _strides(dx)
+    kept = [i for i in range(nd) if i != dim]
+    env.lib.max_backward_f32(_ptr(g), _ptr(indices_tensor), _ptr(dx), _numel(tensor.shape), len(kept), _ll([tensor.shape[i] for i in kept]),
+                             _ll([st[i] for i in kept]), st[dim], env.stream())
+    return [dx]
+
+
+@_reg("cuda", "eq")
+def cuda_eq(x, y):
+    """int8 tensor of element-wise equality (``mytorch/backends/cuda/ops/eq.py:9``)."""
+    from mytorch_b200.dtype import int8
+    from mytorch_b200.tensor import InvalidDataTypeError, MismatchShapesError
+
+    if x.shape != y.shape:
+        raise MismatchShapesError([x.shape, y.shape])
+    kinds = {float32: 0, int64: 1}
+    if x.dtype not in kinds or y.dtype is not x.dtype:
+        raise InvalidDataTypeError(x.dtype)
+    env = _env(x)
+    out = _T()(shape=x.shape, dtype=int8, device=x.device)
+    env.lib.eq_strided(kinds[x.dtype], len(x.shape), _ll(x.shape), _ll(_strides(x)), _ll(_strides(y)), _ptr(x), _ptr(y), _ptr(out), env.stream())
+    return out
+
+
+def _bmm_into(env, batch, m, n, k, a, ta, b, tb, c):
+    """c[i] = op(a[i]) op(b[i]) for i < batch; dense 3-D operands, one GEMM per batch entry."""
+    sa, sb, sc = 4 * (a.shape[1] * a.shape[2]), 4 * (b.shape[1] * b.shape[2]), 4 * m * n
+    for i in range(batch):
+        env.lib.gemm_f32(m, n, k, _ptr(a) + i * sa, ta, _ptr(b) + i * sb, tb, None, 0, _ptr(c) + i * sc, env.stream())
+
+
+@_reg("cuda", "bmm")
+def cuda_bmm(x, y):
+    """[B,M,K] x [B,K,N] -> [B,M,N] (``mytorch/backends/cuda/ops/mm.py:131-138``)."""
+    _f32(x, y)
+    from mytorch_b200.tensor import MismatchShapesError
+
+    if len(x.shape) != 3 or len(y.shape) != 3 or x.shape[0] != y.shape[0] or x.shape[2] != y.shape[1]:
+        raise MismatchShapesError([x.shape, y.shape])
+    env = _env(x)
+    bsz, m, k = x.shape
+    n = y.shape[2]
+    z = _new((bsz, m, n), x)
+    _bmm_into(env, bsz, m, n, k, x, 0, y, 0, z)
+    return z
+
+
+@_reg("cuda", "bmm_backward")
+def cuda_bmm_backward(output_grad, x, y):
+    env = _env(x)
+    bsz, m, k = x.shape
+    n = y.shape[2]
+    dx, dy = _new(x.shape, x), _new(y.shape, y)
+    _bmm_into(env, bsz, m, k, n, output_grad, 0, y, 1, dx)   # dx[i] = dz[i] y[i]^T
+    _bmm_into(env, bsz, k, n, m, x, 1, output_grad, 0, dy)   # dy[i] = x[i]^T dz[i]
+    return dx, dy
 
 
 # ---------------------------------------------------------------------------- reductions

@@ -125,6 +125,8 @@ __global__ void __launch_bounds__(kThreads) strided_binary_kernel(float* __restr
     else if (OP == 2) v = x * y;
     else if (OP == 3) v = x / y;
     else if (OP == 4) v = powf(x, y);
+    else if (OP == 6) v = y * powf(x, y - 1.f);   // d(x^y)/dx
+    else if (OP == 7) v = powf(x, y) * logf(x);   // d(x^y)/dy
     else v = x * alpha;  // OP == 5: strided copy (alpha 1) / scaled broadcast
     out[oo] = v;
   }
@@ -162,6 +164,12 @@ __global__ void cast_f32_i64_kernel(long long* out, const float* in, long long n
   long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
   long long stride = (long long)gridDim.x * blockDim.x;
   for (; i < n; i += stride) out[i] = (long long)in[i];
+}
+
+__global__ void cast_i8_f32_kernel(float* out, const signed char* in, long long n) {
+  long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  long long stride = (long long)gridDim.x * blockDim.x;
+  for (; i < n; i += stride) out[i] = (float)in[i];
 }
 
 int transpose_planes(float* dst, const float* src, int batch, int rows, int cols, cudaStream_t s) {
@@ -265,10 +273,11 @@ MTB_API int mtb_add_bias_rows_f32(const float* x, const float* bias, float* y, l
 }
 
 // Generic broadcast binary op over up to 6 logical dimensions. Strides are in elements; a stride
-// of 0 broadcasts. op: 0 add (x + alpha*y), 1 sub (x - alpha*y), 2 mul, 3 div, 4 pow, 5 alpha*x (y unused).
+// of 0 broadcasts. op: 0 add (x + alpha*y), 1 sub (x - alpha*y), 2 mul, 3 div, 4 pow, 5 alpha*x (y unused),
+// 6 y*x^(y-1) and 7 x^y*ln(x) (the two partial derivatives of pow).
 MTB_API int mtb_binary_strided_f32(int op, int ndim, const long long* shape, const long long* x_strides, const long long* y_strides,
                                    const long long* z_strides, const float* x, const float* y, float* z, float alpha, void* stream) {
-  MTB_REQUIRE(ndim >= 0 && ndim <= 6 && op >= 0 && op <= 5 && x && z && (y || op == 5), "binary_strided: bad arguments");
+  MTB_REQUIRE(ndim >= 0 && ndim <= 6 && op >= 0 && op <= 7 && x && z && (y || op == 5), "binary_strided: bad arguments");
   Strides6 s;
   s.ndim = ndim;
   long long n = 1;
@@ -288,6 +297,8 @@ MTB_API int mtb_binary_strided_f32(int op, int ndim, const long long* shape, con
     case 2: strided_binary_kernel<2><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
     case 3: strided_binary_kernel<3><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
     case 4: strided_binary_kernel<4><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
+    case 6: strided_binary_kernel<6><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
+    case 7: strided_binary_kernel<7><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
     default: strided_binary_kernel<5><<<grid, kThreads, 0, st>>>(z, x, y, n, s, alpha); break;
   }
   MTB_LAUNCH_CHECK("strided_binary_kernel");
@@ -314,6 +325,7 @@ MTB_API int mtb_cast(int kind, const void* src, void* dst, long long n, void* st
   if (kind == 0) cast_i32_i64_kernel<<<grid, kThreads, 0, st>>>((long long*)dst, (const int*)src, n);
   else if (kind == 1) cast_i64_f32_kernel<<<grid, kThreads, 0, st>>>((float*)dst, (const long long*)src, n);
   else if (kind == 2) cast_f32_i64_kernel<<<grid, kThreads, 0, st>>>((long long*)dst, (const float*)src, n);
+  else if (kind == 3) cast_i8_f32_kernel<<<grid, kThreads, 0, st>>>((float*)dst, (const signed char*)src, n);
   else return mtb_fail(MTB_ERR_UNSUPPORTED, "cast kind %d", kind);
   MTB_LAUNCH_CHECK("cast kernel");
   return MTB_OK;

@@ -1,4 +1,4 @@
-from .batch_norm import BatchNorm2d, BatchNormAddReLU2d, BatchNormReLU2d
+from .batch_norm import BatchNorm1d, BatchNorm2d, BatchNormAddReLU2d, BatchNormReLU2d
 from .conv import Conv2d
 from .linear import Linear
 from .max_pool import MaxPool2d

@@ -54,3 +54,18 @@ class BatchNormAddReLU2d(BatchNorm2d):
     def forward(self, x, residual):
         return _batch_norm2d_add_relu(x, residual, self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean,
                                       self.running_var)
+
+
+class BatchNorm1d(BatchNorm2d):
+    """BatchNorm over [N, C] or [N, C, L] inputs (``mytorch/nn/batch_norm.py:92-106``): the same per-channel
+    statistics over every non-channel dimension, computed by the BatchNorm2d kernels on the input viewed
+    as [N, C, L, 1]."""
+
+    def forward(self, x):
+        if len(x.shape) not in (2, 3):
+            raise RuntimeError(f"BatchNorm1d expects a 2-D or 3-D input, got shape {x.shape}")
+        n, c = x.shape[0], x.shape[1]
+        length = x.shape[2] if len(x.shape) == 3 else 1
+        y = _batch_norm2d(x.reshape((n, c, length, 1)), self.weight, self.bias, self.eps, self.training, self.momentum, self.running_mean,
+                          self.running_var)
+        return y.reshape(x.shape)

@@ -1,4 +1,4 @@
-"""mm / permute / reshape front-ends (signatures of ``mytorch/ops/basic_ops.py:12-106``)."""
+"""mm / bmm / permute / reshape front-ends (signatures of ``mytorch/ops/basic_ops.py:12-106``)."""
 from mytorch_b200.ops._common import dispatch, grad_enabled, record, tracker
 from mytorch_b200.tensor import MismatchDevicesError, Tensor
 
@@ -16,6 +16,23 @@ def mm_backward(output_grad, x, y):
     if not (output_grad.device == x.device == y.device):
         raise MismatchDevicesError([output_grad.device, x.device, y.device])
     x_grad, y_grad = dispatch(x.device, "mm_backward")(output_grad, x, y)
+    return [x_grad, y_grad]
+
+
+def bmm(x: Tensor, y: Tensor) -> Tensor:
+    """Batched matrix product [B,M,K] x [B,K,N] (``mytorch/ops/basic_ops.py:39-63``)."""
+    if x.device != y.device:
+        raise MismatchDevicesError([x.device, y.device])
+    z = dispatch(x.device, "bmm")(x, y)
+    z.requires_grad = grad_enabled(x, y)
+    return record("bmm", [x, y], z)
+
+
+@tracker.register_backward_function("bmm")
+def bmm_backward(output_grad, x, y):
+    if not (output_grad.device == x.device == y.device):
+        raise MismatchDevicesError([output_grad.device, x.device, y.device])
+    x_grad, y_grad = dispatch(x.device, "bmm_backward")(output_grad, x, y)
     return [x_grad, y_grad]
 
 

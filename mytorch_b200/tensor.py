@@ -283,5 +283,15 @@ class Tensor:
     def __rpow__(self, other):
         return self._binary("pow", other, True)
 
+    def max(self, dim=None, keepdim=False):
+        from mytorch_b200.ops.max import max as func
+
+        return func(self, dim, keepdim)
+
+    def eq(self, other):
+        from mytorch_b200.ops.eq import eq as func
+
+        return func(self, self._cast_other_to_tensor(other))
+
     def backward(self):
         DAGTracker.instance().backward(self)

@@ -309,3 +309,52 @@ def uniform_init(shape, seed, a, b, dtype=np.float32):
     """mytorch/backends/cpu/ops/elementwise_ops.py:17-22 (global NumPy seed, then uniform)."""
     np.random.seed(seed)
     return np.random.uniform(low=a, high=b, size=shape).astype(dtype)
+
+
+# ---------------------------------------------------------------------------- operators beside the training step
+
+def div_backward(dy, x, y):
+    """mytorch/backends/cpu/ops/broadcast_binary_ops.py:108-115 (with the reductions of _backward_cpu, :21-33)."""
+    return _reduce_to(1 / y * dy, x.shape), _reduce_to(-x / (y ** 2) * dy, y.shape)
+
+
+def pow_backward(dy, x, y):
+    """mytorch/backends/cpu/ops/broadcast_binary_ops.py:130-137."""
+    return _reduce_to(y * np.power(x, y - 1) * dy, x.shape), _reduce_to(np.power(x, y) * np.log(x) * dy, y.shape)
+
+
+def max_forward(x, dim, keepdim):
+    """mytorch/backends/cpu/ops/max.py:7-23: values and, for an integer ``dim``, int64 argmax indices
+    (first maximum).  With ``dim=None`` the CUDA backend (mytorch/backends/cuda/ops/max.py:15-16) reduces
+    over every dimension and records the index into the flattened tensor."""
+    values = np.max(x, axis=dim, keepdims=keepdim).astype(x.dtype)
+    if dim is None:
+        return values, np.argmax(x).astype(np.int64).reshape(values.shape)
+    return values, np.argmax(x, axis=dim, keepdims=keepdim).astype(np.int64)
+
+
+def max_backward(dy, indices, x_shape, dim, keepdim):
+    """mytorch/backends/cuda/ops/max.py:75-120: the gradient goes to the recorded index, zeros elsewhere."""
+    dx = np.zeros(x_shape, dtype=dy.dtype)
+    if dim is None:
+        dx.reshape(-1)[int(np.asarray(indices).reshape(-1)[0])] = np.asarray(dy).reshape(-1)[0]
+        return dx
+    idx = indices if keepdim else np.expand_dims(indices, dim)
+    g = dy if keepdim else np.expand_dims(dy, dim)
+    np.put_along_axis(dx, idx, g, axis=dim)
+    return dx
+
+
+def eq_forward(x, y):
+    """mytorch/backends/cpu/ops/eq.py:9-19."""
+    return (x == y).astype(np.int8)
+
+
+def bmm_forward(x, y):
+    """mytorch/backends/cpu/ops/mm.py:26-31."""
+    return np.matmul(x, y)
+
+
+def bmm_backward(dy, x, y):
+    """mytorch/backends/cpu/ops/mm.py:34-47."""
+    return np.matmul(dy, np.transpose(y, (0, 2, 1))), np.matmul(np.transpose(x, (0, 2, 1)), dy)

@@ -358,6 +358,46 @@ def dp_cases():
     np.savez_compressed(os.path.join(OUT, "data_parallel.npz"), **out)
 
 
+def extra_op_cases():
+    """Operators beside the training step: div / pow gradients (with broadcasting), bmm, eq, max along a
+    dimension, BatchNorm1d, all through the reference's public API on its CPU backend."""
+    import mytorch
+
+    out = {}
+    rng = np.random.default_rng(15)
+    for i, (xs, ys) in enumerate([((4, 6), (4, 6)), ((4, 6), (6,)), ((2, 3, 4, 5), (1, 3, 1, 1))]):
+        x, y = rng.uniform(0.5, 2.0, xs).astype(f32), rng.uniform(0.5, 2.0, ys).astype(f32)
+        dz = rng.standard_normal(np.broadcast_shapes(xs, ys)).astype(f32)
+        for name, fn in (("div", lambda a, b: a / b), ("pow", lambda a, b: a ** b)):
+            xt, yt = T(x, True), T(y, True)
+            z = fn(xt, yt)
+            backward_with(z, dz)
+            out.update({f"{name}{i}_x": x, f"{name}{i}_y": y, f"{name}{i}_dz": dz, f"{name}{i}_z": npy(z),
+                        f"{name}{i}_dx": npy(xt.grad), f"{name}{i}_dy": npy(yt.grad)})
+    x, y = rng.standard_normal((3, 5, 7)).astype(f32), rng.standard_normal((3, 7, 6)).astype(f32)
+    dz = rng.standard_normal((3, 5, 6)).astype(f32)
+    xt, yt = T(x, True), T(y, True)
+    z = mytorch.bmm(xt, yt)
+    backward_with(z, dz)
+    out.update(bmm_x=x, bmm_y=y, bmm_dz=dz, bmm_z=npy(z), bmm_dx=npy(xt.grad), bmm_dy=npy(yt.grad))
+    a, b = rng.integers(0, 3, (4, 9)).astype(f32), rng.integers(0, 3, (4, 9)).astype(f32)
+    out.update(eq_a=a, eq_b=b, eq_z=npy(T(a).eq(T(b))))
+    m = rng.integers(-4, 5, (3, 5, 6)).astype(f32)
+    for dim in (0, 1, 2):
+        v, idx = T(m).max(dim, False)
+        out.update({"max_x": m, f"max{dim}_v": npy(v), f"max{dim}_i": npy(idx)})
+    for i, shape in enumerate([(16, 12), (6, 12, 10)]):
+        x = (1.0 + rng.standard_normal(shape)).astype(f32)
+        dy = rng.standard_normal(shape).astype(f32)
+        bn = nn.BatchNorm1d(12)
+        xt = T(x, True)
+        yv = bn(xt)
+        backward_with(yv, dy)
+        out.update({f"bn1d{i}_x": x, f"bn1d{i}_dy": dy, f"bn1d{i}_y": npy(yv), f"bn1d{i}_dx": npy(xt.grad), f"bn1d{i}_dg": npy(bn.weight.grad),
+                    f"bn1d{i}_db": npy(bn.bias.grad), f"bn1d{i}_rm": npy(bn.running_mean), f"bn1d{i}_rv": npy(bn.running_var)})
+    np.savez_compressed(os.path.join(OUT, "extra_ops.npz"), **out)
+
+
 def checkpoint_case():
     """A checkpoint written by the reference's own ``mytorch.save`` after one SGD-momentum step of a small
     Conv-BN-ReLU-MaxPool-Linear net (model and optimizer state dicts), and what the reference computes
@@ -397,7 +437,7 @@ def checkpoint_case():
 
 if __name__ == "__main__":
     only = sys.argv[2:]  # optional: names of the fixture groups to regenerate
-    groups = {"conv": conv_cases, "bn": bn_cases, "pool": pool_cases, "misc": misc_cases, "models": model_cases, "dp": dp_cases, "checkpoint": checkpoint_case}
+    groups = {"conv": conv_cases, "bn": bn_cases, "pool": pool_cases, "misc": misc_cases, "models": model_cases, "dp": dp_cases, "checkpoint": checkpoint_case, "extra": extra_op_cases}
     for name, fn in groups.items():
         if not only or name in only:
             fn()

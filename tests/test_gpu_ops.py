@@ -422,3 +422,83 @@ def test_conv_epilogue_hands_batch_norm_its_statistics(g, cfg, monkeypatch):
         assert rel_err(got[1], rmean.reshape(-1)) < FP32_TOL and rel_err(got[2], rvar.reshape(-1)) < 2 * FP32_TOL
         assert rel_err(got[3], rrm) < FP32_TOL and rel_err(got[4], rrv) < 2 * FP32_TOL
     assert rel_err(outs[0][1], outs[1][1]) < FP32_TOL and rel_err(outs[0][2], outs[1][2]) < 2 * FP32_TOL
+
+
+def test_max_with_indices_and_its_backward(g):
+    import mytorch_b200 as mt
+
+    rng = np.random.default_rng(21)
+    cases = [((7, 13), 1, False), ((7, 13), 0, True), ((3, 5, 6, 4), 1, False), ((3, 5, 6, 4), 3, True), ((3, 5, 6, 4), -2, False),
+             ((4, 300), 1, False), ((2, 3, 4), None, False), ((3, 5, 6, 4), None, False)]
+    for shape, dim, keep in cases:
+        x = rng.integers(-4, 5, shape).astype(np.float32)   # many ties: the first maximum must win
+        xt = g.dev(x, True)
+        out = mt.max(xt, dim, keep)
+        rv, ri = O.max_forward(x, dim, keep)
+        if dim is None:
+            values = out
+            assert np.array_equal(g.host(values.detach()), rv)
+        else:
+            values, indices = out
+            assert np.array_equal(g.host(values.detach()), rv) and np.array_equal(g.host(indices), ri)
+        dy = rng.standard_normal(rv.shape if rv.shape else (1,)).astype(np.float32).reshape(rv.shape)
+        node = values._grad_node
+        (dx,) = g.op("max_backward")(g.dev(dy), node.helpers[0], xt, dim, keep)
+        assert np.array_equal(g.host(dx), O.max_backward(dy, O.max_forward(x, dim, keep)[1], x.shape, dim, keep))
+
+
+def test_eq_bmm_and_the_remaining_binary_gradients(g):
+    import mytorch_b200 as mt
+
+    rng = np.random.default_rng(22)
+    for shape in [(5, 7), (2, 3, 4, 5)]:
+        a = rng.integers(0, 3, shape).astype(np.float32)
+        b = rng.integers(0, 3, shape).astype(np.float32)
+        assert np.array_equal(g.host(g.dev(a).eq(g.dev(b))), O.eq_forward(a, b))
+    ia, ib = rng.integers(0, 4, (33,)).astype(np.int64), rng.integers(0, 4, (33,)).astype(np.int64)
+    assert np.array_equal(g.host(mt.eq(g.dev(ia), g.dev(ib))), O.eq_forward(ia, ib))
+    # batched product: a CUDA-core sized case and a tensor-core sized one
+    for bsz, m, k, n in [(3, 5, 7, 6), (2, 64, 96, 48)]:
+        x = rng.standard_normal((bsz, m, k)).astype(np.float32)
+        y = rng.standard_normal((bsz, k, n)).astype(np.float32)
+        dz = rng.standard_normal((bsz, m, n)).astype(np.float32)
+        xt, yt = g.dev(x, True), g.dev(y, True)
+        assert rel_err(g.host(mt.bmm(xt, yt).detach()), O.bmm_forward(x, y)) < TF32_TOL
+        dx, dy = g.op("bmm_backward")(g.dev(dz), xt, yt)
+        rdx, rdy = O.bmm_backward(dz, x, y)
+        assert rel_err(g.host(dx), rdx) < TF32_TOL and rel_err(g.host(dy), rdy) < TF32_TOL
+    # div / pow gradients, same shape and broadcast
+    for xs, ys in [((4, 6), (4, 6)), ((4, 6), (6,)), ((2, 3, 4, 5), (1, 3, 1, 1))]:
+        x = rng.uniform(0.5, 2.0, xs).astype(np.float32)
+        y = rng.uniform(0.5, 2.0, ys).astype(np.float32)
+        dz = rng.standard_normal(np.broadcast_shapes(xs, ys)).astype(np.float32)
+        for name, ref in (("div_backward", O.div_backward), ("pow_backward", O.pow_backward)):
+            gx, gy = g.op(name)(g.dev(dz), g.dev(x), g.dev(y))
+            rx, ry = ref(dz, x, y)
+            assert rel_err(g.host(gx), rx) < 2 * FP32_TOL and rel_err(g.host(gy), ry) < 2 * FP32_TOL, (name, xs, ys)
+    # through the tape
+    x, y = g.dev(rng.uniform(0.5, 2.0, (3, 4)).astype(np.float32), True), g.dev(rng.uniform(0.5, 2.0, (4,)).astype(np.float32), True)
+    ((x / y) ** y).sum().backward()
+    assert x.grad.shape == (3, 4) and y.grad.shape == (4,)
+
+
+def test_batch_norm_1d(g):
+    import mytorch_b200.nn as nn
+
+    rng = np.random.default_rng(23)
+    for shape in [(16, 12), (6, 12, 10)]:
+        x = (1.0 + rng.standard_normal(shape)).astype(np.float32)
+        dy = rng.standard_normal(shape).astype(np.float32)
+        bn = nn.BatchNorm1d(12)
+        bn.to(g.DEV)
+        xt = g.dev(x, True)
+        y = bn(xt)
+        (y * g.dev(dy)).sum().backward()
+        x4 = x.reshape(shape[0], 12, -1, 1)
+        ry, mean, var, rm, rv = O.batch_norm2d_forward(x4, np.ones(12, np.float32), np.zeros(12, np.float32), 1e-5, True, 0.1,
+                                                        np.zeros(12, np.float32), np.ones(12, np.float32))
+        rdx, rdg, rdb = O.batch_norm2d_backward(dy.reshape(x4.shape), mean, var, x4, np.ones(12, np.float32), 1e-5)
+        assert rel_err(g.host(y.detach()), ry.reshape(shape)) < FP32_TOL
+        assert rel_err(g.host(xt.grad), rdx.reshape(shape)) < 2 * FP32_TOL
+        assert rel_err(g.host(bn.weight.grad), rdg) < 3 * FP32_TOL and rel_err(g.host(bn.bias.grad), rdb) < 3 * FP32_TOL
+        assert rel_err(g.host(bn.running_mean), rm) < FP32_TOL and rel_err(g.host(bn.running_var), rv) < FP32_TOL

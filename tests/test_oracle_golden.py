@@ -3,6 +3,7 @@ import numpy as np
 
 from conftest import load_golden, rel_err, summarize
 from oracle import models, ops
+from oracle import ops as O
 
 TOL = 2e-6  # both sides are fp32 results of float64/fp32 NumPy arithmetic
 
@@ -141,3 +142,32 @@ def test_bn_relu_pool_block_matches_reference():
     assert rel_err(r["dx"], g["block/dx"]) < 1e-5
     assert rel_err(r["dgamma"], g["block/dgamma"]) < 1e-5 and rel_err(r["dbeta"], g["block/dbeta"]) < 1e-5
     assert rel_err(r["running_mean"], g["block/rm"]) < TOL and rel_err(r["running_var"], g["block/rv"]) < TOL
+
+
+def test_operators_beside_the_training_step_match_reference():
+    """div / pow gradients, bmm, eq, max along a dimension and BatchNorm1d of the oracle against fixtures
+    written by the reference's CPU backend (tests/golden/make_golden.py, ``extra_op_cases``)."""
+    gd = load_golden("extra_ops")
+    for i in range(3):
+        for name, fwd, bwd in (("div", lambda a, b: a / b, O.div_backward), ("pow", np.power, O.pow_backward)):
+            x, y, dz = gd[f"{name}{i}_x"], gd[f"{name}{i}_y"], gd[f"{name}{i}_dz"]
+            assert rel_err(fwd(x, y), gd[f"{name}{i}_z"]) < 1e-6
+            dx, dy = bwd(dz, x, y)
+            assert dx.shape == x.shape and dy.shape == y.shape
+            assert rel_err(dx, gd[f"{name}{i}_dx"]) < 1e-5 and rel_err(dy, gd[f"{name}{i}_dy"]) < 1e-5
+    assert rel_err(O.bmm_forward(gd["bmm_x"], gd["bmm_y"]), gd["bmm_z"]) < 1e-6
+    dx, dy = O.bmm_backward(gd["bmm_dz"], gd["bmm_x"], gd["bmm_y"])
+    assert rel_err(dx, gd["bmm_dx"]) < 1e-6 and rel_err(dy, gd["bmm_dy"]) < 1e-6
+    assert np.array_equal(O.eq_forward(gd["eq_a"], gd["eq_b"]), gd["eq_z"])
+    for dim in (0, 1, 2):
+        v, i = O.max_forward(gd["max_x"], dim, False)
+        assert np.array_equal(v, gd[f"max{dim}_v"]) and np.array_equal(i, gd[f"max{dim}_i"])
+    for i in range(2):
+        x, dy = gd[f"bn1d{i}_x"], gd[f"bn1d{i}_dy"]
+        x4 = x.reshape(x.shape[0], 12, -1, 1)
+        ones, zeros = np.ones(12, np.float32), np.zeros(12, np.float32)
+        y, mean, var, rm, rv = O.batch_norm2d_forward(x4, ones, zeros, 1e-5, True, 0.1, zeros, ones)
+        dx, dg, db = O.batch_norm2d_backward(dy.reshape(x4.shape), mean, var, x4, ones, 1e-5)
+        assert rel_err(y.reshape(x.shape), gd[f"bn1d{i}_y"]) < 1e-5 and rel_err(dx.reshape(x.shape), gd[f"bn1d{i}_dx"]) < 2e-5
+        assert rel_err(dg, gd[f"bn1d{i}_dg"]) < 2e-5 and rel_err(db, gd[f"bn1d{i}_db"]) < 2e-5
+        assert rel_err(rm, gd[f"bn1d{i}_rm"]) < 1e-5 and rel_err(rv, gd[f"bn1d{i}_rv"]) < 1e-5
