@@ -251,7 +251,7 @@ def reference_first_loss(world):
         return float(gd[key]) if key in gd else None
 
 
-def kernel_legs(torch, env, peaks):
+def kernel_legs(env, peaks):
     """Time the dominant kernels alone (CUDA events on the launch stream, buffers rotated so that
     every launch reads data that is not in L2).  Returns (roofline dict, per-kernel dict)."""
     import mytorch_b200 as mt
@@ -259,19 +259,20 @@ def kernel_legs(torch, env, peaks):
 
     op = lambda name: BackendDispatcher.instance().dispatch("cuda", name)
     rng = np.random.default_rng(1)
-    stream = torch.cuda.current_stream()
+    from mytorch_b200.backends.cuda.env import Event
 
     def timed(fn, reps=10, warm=3):
+        """seconds per call: CUDA events on the compute stream the kernels are launched on"""
         for i in range(warm):
             fn(i)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        env.synchronize()
+        e0, e1 = Event(timing=True), Event(timing=True)
+        e0.record()
         for i in range(reps):
             fn(i)
-        e1.record(stream)
-        torch.cuda.synchronize()
-        return e0.elapsed_time(e1) / reps * 1e-3
+        e1.record()
+        env.synchronize()
+        return e0.elapsed_ms(e1) / reps * 1e-3
 
     out = {}
     # dominant conv layer of the step: 64->64 3x3 on 32x32 at the full batch (4 of the 20 convs, 27% of the FLOPs)
@@ -368,29 +369,31 @@ def kernel_legs(torch, env, peaks):
 
 
 def run_gpu_arm(args):
-    import torch
-    import torch.distributed as dist
-
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch = dist = None
+    if world > 1:  # PyTorch only carries the NCCL process group; one GPU runs without it
+        import torch
+        import torch.distributed as dist
     if world != args.gpus:
         if world == 1 and args.gpus > 1:
             sys.exit(f"--gpus {args.gpus} needs torchrun: python -m torch.distributed.run --nproc-per-node {args.gpus} bench.py ...")
-    torch.cuda.set_device(local)
     if world > 1:
+        torch.cuda.set_device(local)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device(f"cuda:{local}"))
 
     import mytorch_b200 as mt
     import mytorch_b200.nn.functional as F
-    from mytorch_b200.backends.cuda.env import CudaEnv
+    from mytorch_b200.backends.cuda.env import CudaEnv, Event, PinnedBuffer
     from mytorch_b200.cuda_graph import StepGraph
     from mytorch_b200.examples.models import ResNet18Cifar
     from mytorch_b200.optim import SGD
     from mytorch_b200.parallel import DataParallel, shard_bounds
 
     env = CudaEnv.instance()
+    env.set_device(local)
     dev = f"cuda:{local}"
     peaks = measured_peaks()
 
@@ -400,8 +403,13 @@ def run_gpu_arm(args):
     lo, hi = shard_bounds(GLOBAL_BATCH, rank, world)
     local_batch = hi - lo
     # a few distinct host batches in pinned memory for the end-to-end leg
-    host_x = [torch.from_numpy(np.roll(x_all, s, axis=0)[lo:hi].copy()).pin_memory() for s in range(4)]
-    host_t = [torch.from_numpy(np.roll(t_all, s, axis=0)[lo:hi].copy()).pin_memory() for s in range(4)]
+    pinned = []
+    for s in range(4):
+        px, pt = PinnedBuffer((local_batch, 3, 32, 32), np.float32), PinnedBuffer((local_batch,), np.int64)
+        px.array[...] = np.roll(x_all, s, axis=0)[lo:hi]
+        pt.array[...] = np.roll(t_all, s, axis=0)[lo:hi]
+        pinned.append((px, pt))
+    host_x, host_t = [p[0].array for p in pinned], [p[1].array for p in pinned]
 
     mt.manual_seed(SEED)
     net = ResNet18Cifar()
@@ -420,7 +428,7 @@ def run_gpu_arm(args):
         return loss
 
     def barrier():
-        torch.cuda.synchronize()
+        env.synchronize()
         if world > 1:
             dist.barrier()
             torch.cuda.synchronize()
@@ -431,7 +439,7 @@ def run_gpu_arm(args):
         first_loss = float(fl.item()) / world
     loss_ref = reference_first_loss(world)
     step()
-    torch.cuda.synchronize()
+    env.synchronize()
     runner = None
     if not args.no_graph:
         before = env.lib.launches
@@ -462,20 +470,22 @@ def run_gpu_arm(args):
         upload_into(ts, host_t[i % 4])
         return step().item()
 
-    stream = torch.cuda.current_stream()
-
     def timed_region(body, steps):
+        """milliseconds for `steps` steps: CUDA events on the compute stream, barrier + synchronise on both
+        sides, the maximum over ranks"""
         barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record(stream)
+        e0, e1 = Event(timing=True), Event(timing=True)
+        e0.record()
         for i in range(steps):
             body(i)
-        e1.record(stream)
+        e1.record()
         barrier()
-        ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+        elapsed = e0.elapsed_ms(e1)
         if world > 1:
+            ms = torch.tensor([elapsed], device=dev)
             dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-        return float(ms.item())
+            elapsed = float(ms.item())
+        return elapsed
 
     for _ in range(max(args.warmup, 3)):
         run_resident()
@@ -504,8 +514,10 @@ def run_gpu_arm(args):
 
     roof, kernels, cpu = None, None, None
     if rank == 0 and world == 1 and not args.skip_legs:
-        roof, kernels = kernel_legs(torch, env, peaks)
+        roof, kernels = kernel_legs(env, peaks)
         try:
+            import torch
+
             a = torch.randn(8192, 8192, device=dev)
             b = torch.randn(8192, 8192, device=dev)
             torch.backends.cuda.matmul.allow_tf32 = True
@@ -534,7 +546,7 @@ def run_gpu_arm(args):
                        "cuda_graph": not args.no_graph,
                        "l2": "no flush: one step streams ~1.3 GB of activations per pass, 10x the 126 MB L2"},
             "step_tflops": step_flops / (ms_per_step * 1e-3) / 1e12,
-            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(host_x[0].numel() * 4 + host_t[0].numel() * 8) * world,
+            "e2e": {"value": e2e_value, "unit": "images/s", "h2d_bytes_per_step": int(host_x[0].nbytes + host_t[0].nbytes) * world,
                     "d2h_bytes_per_step": 4 * world},
             "gpu_launches": calls_per_step * args.steps,
             "gpu_launches_note": "C-ABI calls per step x steps; each call enqueues 1-3 kernels of libmytorch_b200.so",
@@ -578,11 +590,9 @@ def main():
     args = ap.parse_args()
     GLOBAL_BATCH = args.global_batch
     if args.only_legs:
-        import torch
-
         from mytorch_b200.backends.cuda.env import CudaEnv
 
-        roof, kernels = kernel_legs(torch, CudaEnv.instance(), measured_peaks())
+        roof, kernels = kernel_legs(CudaEnv.instance(), measured_peaks())
         print(json.dumps({"roofline": roof, "kernels": kernels}))
     elif args.impl == "reference":
         run_reference_arm(args)

@@ -3,8 +3,9 @@
  *
  * Conventions
  *  - Every pointer is a raw device pointer unless a comment says "host".  The caller owns all
- *    buffers, including scratch ("workspace"); the library allocates nothing and keeps no
- *    reference after a call returns.
+ *    buffers, including scratch ("workspace"); the kernels allocate nothing and keep no
+ *    reference after a call returns.  Memory comes from the pool in the runtime section below
+ *    (or from any other allocator: the kernels only see pointers).
  *  - 4-D activations and convolution weights are channels-last: x[N][H][W][C],
  *    w[Cout][KH][KW][Cin].  Everything else is dense row-major.
  *  - `stream` is a cudaStream_t; work is enqueued on it and the call returns without
@@ -38,6 +39,45 @@ int mtb_tc_status(int* status_out);
  * the wait runs out, `code` (non-zero) lands in the status word, tensor memory is freed and the kernel
  * returns.  Nothing traps; the context stays usable. */
 int mtb_tc_wait_selftest(long long limit_cycles, int code, void* stream);
+
+/* ---- device memory, copies, streams, events, graphs (replace the reference's runtime layer:
+ *      CudaMemory / allocate_memory / transfer_memory, mytorch/backends/cuda/env.py:524-580; the size-keyed
+ *      caching allocator, mytorch/backends/cuda/memory_allocator.py:16-51; stream handling, env.py:61-94) ----
+ * mtb_malloc serves the current device from a pool of freed blocks keyed by size (a step that repeats its
+ * allocation pattern gets the same addresses again and never reaches the driver); it returns NULL on failure.
+ * The pool does no stream tracking: memory used on another stream than the one its owner computes on must be
+ * kept alive until that stream is done.  Between mtb_graph_begin_capture and mtb_graph_end_capture work
+ * enqueued on `stream` is recorded instead of run, and every block handed out belongs to the graph until
+ * mtb_graph_destroy: it can be reused inside the capture but never by anything outside it. */
+void* mtb_malloc(long long nbytes);
+int mtb_free(void* ptr);
+long long mtb_pool_reserved_bytes(void);
+long long mtb_pool_in_use_bytes(void);
+int mtb_pool_trim(void);
+int mtb_set_device(int device);
+int mtb_get_device(int* device);              /* HOST out */
+int mtb_device_count(int* count);             /* HOST out */
+int mtb_device_synchronize(void);
+int mtb_mem_get_info(long long* free_bytes, long long* total_bytes); /* HOST out */
+int mtb_memcpy_h2d_async(void* dst, const void* src_host, long long nbytes, void* stream);
+int mtb_memcpy_d2h_async(void* dst_host, const void* src, long long nbytes, void* stream);
+int mtb_memcpy_d2d_async(void* dst, const void* src, long long nbytes, void* stream);
+int mtb_memset_async(void* dst, int value, long long nbytes, void* stream);
+void* mtb_host_alloc_pinned(long long nbytes);
+int mtb_host_free_pinned(void* ptr);
+void* mtb_stream_create(void);
+int mtb_stream_destroy(void* stream);
+int mtb_stream_synchronize(void* stream);
+int mtb_stream_wait_event(void* stream, void* event);
+void* mtb_event_create(int timing);
+int mtb_event_destroy(void* event);
+int mtb_event_record(void* event, void* stream);
+int mtb_event_synchronize(void* event);
+int mtb_event_elapsed_ms(void* start, void* end, float* ms); /* HOST out */
+int mtb_graph_begin_capture(void* stream);
+int mtb_graph_end_capture(void* stream, void** graph_exec_out); /* HOST out */
+int mtb_graph_launch(void* graph_exec, void* stream);
+int mtb_graph_destroy(void* graph_exec);
 
 /* ---- convolution (replaces ConvForwardImplicitGEMM_float32 / ConvBackwardImplicitGEMM_float32,
  *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from

@@ -1,10 +1,12 @@
-"""CUDA runtime glue: the kernel library (ctypes over its C ABI), device memory and streams.
+"""CUDA runtime glue: the kernel library (ctypes over its C ABI), device memory, streams, events.
 
 Plays the role of the reference's ``mytorch/backends/cuda/env.py`` (library loader
 ``:341-393``, ``CudaMemory`` ``:524-561``, ``allocate_memory`` / ``transfer_memory``
-``:564-580``).  Device memory, the current stream and host<->device copies come from PyTorch's
-CUDA runtime (caching allocator, so repeated steps reuse the same blocks and a whole step can
-be captured in a CUDA graph); all arithmetic is done by ``libmytorch_b200.so``.
+``:564-580``) and ``memory_allocator.py:16-51``.  Everything comes from ``libmytorch_b200.so``:
+the arithmetic kernels and the runtime around them (a size-keyed device memory pool whose blocks
+keep their addresses from step to step, asynchronous copies, one compute stream per device,
+events, whole-step graph capture).  This module imports neither PyTorch nor any other CUDA
+binding; ``mytorch_b200.parallel`` alone uses ``torch.distributed`` for the NCCL all-reduce.
 
 There is no fallback: if the library is missing or the device is not sm_100, the first CUDA
 operation raises.
@@ -74,6 +76,36 @@ _SIGNATURES = {
     "mtb_conv2d_wgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_gemm_f32": ([_I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _P], _I),
     "mtb_tc_status": ([_P], _I),
+    # runtime
+    "mtb_malloc": ([_L], _P),
+    "mtb_free": ([_P], _I),
+    "mtb_pool_reserved_bytes": ([], _L),
+    "mtb_pool_in_use_bytes": ([], _L),
+    "mtb_pool_trim": ([], _I),
+    "mtb_set_device": ([_I], _I),
+    "mtb_get_device": ([_P], _I),
+    "mtb_device_count": ([_P], _I),
+    "mtb_device_synchronize": ([], _I),
+    "mtb_mem_get_info": ([_P, _P], _I),
+    "mtb_memcpy_h2d_async": ([_P, _P, _L, _P], _I),
+    "mtb_memcpy_d2h_async": ([_P, _P, _L, _P], _I),
+    "mtb_memcpy_d2d_async": ([_P, _P, _L, _P], _I),
+    "mtb_memset_async": ([_P, _I, _L, _P], _I),
+    "mtb_host_alloc_pinned": ([_L], _P),
+    "mtb_host_free_pinned": ([_P], _I),
+    "mtb_stream_create": ([], _P),
+    "mtb_stream_destroy": ([_P], _I),
+    "mtb_stream_synchronize": ([_P], _I),
+    "mtb_stream_wait_event": ([_P, _P], _I),
+    "mtb_event_create": ([_I], _P),
+    "mtb_event_destroy": ([_P], _I),
+    "mtb_event_record": ([_P, _P], _I),
+    "mtb_event_synchronize": ([_P], _I),
+    "mtb_event_elapsed_ms": ([_P, _P, _P], _I),
+    "mtb_graph_begin_capture": ([_P], _I),
+    "mtb_graph_end_capture": ([_P, _P], _I),
+    "mtb_graph_launch": ([_P, _P], _I),
+    "mtb_graph_destroy": ([_P], _I),
     "mtb_tc_wait_selftest": ([_L, _I, _P], _I),
 }
 
@@ -82,13 +114,21 @@ LIBRARY_PATH = os.environ.get(
     os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))), "lib", "libmytorch_b200.so"),
 )
 
+# entry points that only enqueue or bookkeep: not counted as kernel launches
+_NOT_LAUNCHES = {"mtb_free", "mtb_pool_trim", "mtb_set_device", "mtb_get_device", "mtb_device_count", "mtb_device_synchronize", "mtb_mem_get_info",
+                 "mtb_memcpy_h2d_async", "mtb_memcpy_d2h_async", "mtb_memcpy_d2d_async", "mtb_memset_async", "mtb_host_free_pinned",
+                 "mtb_stream_destroy", "mtb_stream_synchronize", "mtb_stream_wait_event", "mtb_event_destroy", "mtb_event_record",
+                 "mtb_event_synchronize", "mtb_event_elapsed_ms", "mtb_graph_begin_capture", "mtb_graph_end_capture", "mtb_graph_launch",
+                 "mtb_graph_destroy", "mtb_tc_status", "mtb_device_check", "mtb_conv2d_plan_f32"}
+
 
 class NativeError(RuntimeError):
     pass
 
 
 class NativeLibrary:
-    """ctypes view of ``libmytorch_b200.so``; every wrapped call raises on a non-zero status."""
+    """ctypes view of ``libmytorch_b200.so``; every wrapped call raises on a non-zero status (or a
+    NULL pointer from the entry points that return one)."""
 
     def __init__(self, path=LIBRARY_PATH):
         if not os.path.exists(path):
@@ -103,15 +143,31 @@ class NativeLibrary:
             fn = getattr(self._dll, name)
             fn.argtypes = argtypes
             fn.restype = restype
-            setattr(self, name[4:], self._checked(name, fn) if restype is _I and name not in ("mtb_version", "mtb_conv2d_stats_max_rows") else fn)
+            if restype is _P:
+                wrapped = self._pointer(name, fn)
+            elif restype is _I and name not in ("mtb_version", "mtb_conv2d_stats_max_rows"):
+                wrapped = self._checked(name, fn, name not in _NOT_LAUNCHES)
+            else:
+                wrapped = fn
+            setattr(self, name[4:], wrapped)
 
-    def _checked(self, name, fn):
+    def _checked(self, name, fn, counts):
         def call(*args):
             rc = fn(*args)
             if rc != 0:
                 raise NativeError(f"{name} failed ({rc}): {self._dll.mtb_last_error().decode()}")
-            self.launches += 1
+            if counts:
+                self.launches += 1
             return rc
+
+        return call
+
+    def _pointer(self, name, fn):
+        def call(*args):
+            p = fn(*args)
+            if not p:
+                raise NativeError(f"{name} failed: {self._dll.mtb_last_error().decode()}")
+            return p
 
         return call
 
@@ -119,8 +175,51 @@ class NativeLibrary:
         return hasattr(self._dll, name)
 
 
+class Event:
+    """A CUDA event (``timing=True`` to measure elapsed time between two of them)."""
+
+    def __init__(self, timing=False):
+        self._lib = CudaEnv.instance().lib
+        self.handle = self._lib.event_create(int(bool(timing)))
+
+    def record(self, stream=None):
+        self._lib.event_record(self.handle, CudaEnv.instance().stream() if stream is None else stream)
+
+    def synchronize(self):
+        self._lib.event_synchronize(self.handle)
+
+    def elapsed_ms(self, later):
+        ms = ctypes.c_float(0)
+        self._lib.event_elapsed_ms(self.handle, later.handle, ctypes.byref(ms))
+        return ms.value
+
+    def __del__(self):
+        try:
+            self._lib.event_destroy(self.handle)
+        except Exception:
+            pass
+
+
+class PinnedBuffer:
+    """Page-locked host memory, viewed as a NumPy array: copies from it to the device are asynchronous."""
+
+    def __init__(self, shape, np_dtype):
+        self._lib = CudaEnv.instance().lib
+        self.nbytes = int(np.prod(shape, dtype=np.int64)) * np.dtype(np_dtype).itemsize
+        self.ptr = self._lib.host_alloc_pinned(self.nbytes)
+        raw = (ctypes.c_ubyte * max(self.nbytes, 1)).from_address(self.ptr)
+        self.array = np.frombuffer(raw, dtype=np_dtype, count=int(np.prod(shape, dtype=np.int64))).reshape(shape)
+
+    def __del__(self):
+        try:
+            self.array = None
+            self._lib.host_free_pinned(self.ptr)
+        except Exception:
+            pass
+
+
 class CudaEnv:
-    """Per-process CUDA state: the library, and one grow-only scratch buffer per device."""
+    """Per-process CUDA state: the library, one compute stream and one grow-only scratch buffer per device."""
 
     _instance = None
 
@@ -131,21 +230,51 @@ class CudaEnv:
         return cls._instance
 
     def __init__(self):
-        import torch
-
-        if not torch.cuda.is_available():
-            raise NativeError("no CUDA device is available; the cuda backend has no CPU fallback")
-        self.torch = torch
         self.lib = NativeLibrary()
+        count = ctypes.c_int(0)
+        try:
+            self.lib.device_count(ctypes.byref(count))
+        except NativeError as e:
+            raise NativeError(f"no CUDA device is available; the cuda backend has no CPU fallback ({e})") from None
+        if count.value == 0:
+            raise NativeError("no CUDA device is available; the cuda backend has no CPU fallback")
         self.lib.device_check()
+        self._streams = {}
         self._scratch = {}
         self._retired_scratch = []
+        self._capturing = False
+
+    # ---- devices, streams
+    def current_device(self):
+        dev = ctypes.c_int(0)
+        self.lib.get_device(ctypes.byref(dev))
+        return dev.value
+
+    def set_device(self, index):
+        if index is not None and index != self.current_device():
+            self.lib.set_device(int(index))
 
     def stream(self):
-        return self.torch.cuda.current_stream().cuda_stream
+        """The compute stream of the current device: every operator enqueues its work there."""
+        dev = self.current_device()
+        s = self._streams.get(dev)
+        if s is None:
+            s = self._streams[dev] = self.lib.stream_create()
+        return s
+
+    def new_stream(self):
+        return self.lib.stream_create()
+
+    def synchronize(self):
+        self.lib.device_synchronize()
 
     def capturing(self):
-        return bool(self.torch.cuda.is_current_stream_capturing())
+        return self._capturing
+
+    def mem_get_info(self):
+        free, total = ctypes.c_longlong(0), ctypes.c_longlong(0)
+        self.lib.mem_get_info(ctypes.byref(free), ctypes.byref(total))
+        return free.value, total.value
 
     def tensor_core_status(self):
         """Synchronises and returns the status word of the tensor-core kernels (0 = fine; non-zero
@@ -154,59 +283,83 @@ class CudaEnv:
         self.lib.tc_status(ctypes.byref(out))
         return out.value
 
-    def set_device(self, index):
-        if index is not None and index != self.torch.cuda.current_device():
-            self.torch.cuda.set_device(index)
-
-    def alloc(self, nbytes, index=None):
-        dev = self.torch.cuda.current_device() if index is None else index
-        return self.torch.empty((max(int(nbytes), 1),), dtype=self.torch.uint8, device=f"cuda:{dev}")
-
+    # ---- memory
     def workspace(self, nbytes):
         """Scratch for kernels that need it (split-K partials, per-CTA reduction partials).
         One buffer per device, shared by all operators: they run in order on one stream."""
-        dev = self.torch.cuda.current_device()
+        dev = self.current_device()
         buf = self._scratch.get(dev)
-        if buf is None or buf.numel() < nbytes:
+        if buf is None or buf.nbytes < nbytes:
             if buf is not None:
                 # a captured graph may hold this block's address: it is kept for the life of the
-                # process so that the allocator can never hand it to a tensor a replay would overwrite
+                # process so that the pool can never hand it to a tensor a replay would overwrite
                 self._retired_scratch.append(buf)
-            buf = self.alloc(max(int(nbytes), 1 << 20), dev)
+            buf = CudaMemory(dev, max(int(nbytes), 1 << 20))
             self._scratch[dev] = buf
-        return buf.data_ptr(), buf.numel()
+        return buf.ptr, buf.nbytes
 
 
 class CudaMemory:
-    """A device allocation. ``ptr`` is the raw device address; ``read`` / ``write`` move bytes
-    between it and NumPy arrays without interpreting any layout."""
+    """A device allocation from the library's pool. ``ptr`` is the raw device address; ``read`` /
+    ``write`` move bytes between it and NumPy arrays without interpreting any layout."""
 
     def __init__(self, device_index, nbytes):
         env = CudaEnv.instance()
-        self.device_index = env.torch.cuda.current_device() if device_index is None else device_index
+        self.device_index = env.current_device() if device_index is None else device_index
+        env.set_device(self.device_index)
         self.nbytes = int(nbytes)
-        self._buf = env.alloc(self.nbytes, self.device_index)
-        self.ptr = self._buf.data_ptr()
+        self._lib = env.lib
+        self.ptr = env.lib.malloc(max(self.nbytes, 1))
 
     def read(self, shape, np_dtype):
-        torch = CudaEnv.instance().torch
-        n = int(np.prod(shape, dtype=np.int64)) * np.dtype(np_dtype).itemsize
-        host = self._buf[:n].cpu().numpy()
-        return host.view(np_dtype).reshape(shape).copy()
+        env = CudaEnv.instance()
+        env.set_device(self.device_index)
+        out = np.empty(shape, dtype=np_dtype)
+        env.lib.memcpy_d2h_async(out.ctypes.data, self.ptr, out.nbytes, env.stream())
+        env.lib.stream_synchronize(env.stream())
+        return out
 
-    def write(self, array, non_blocking=False):
-        torch = CudaEnv.instance().torch
+    def write(self, array):
+        """Copy a NumPy array in (pageable memory: the call returns once the bytes are staged)."""
+        env = CudaEnv.instance()
+        env.set_device(self.device_index)
         a = np.ascontiguousarray(array)
-        src = torch.from_numpy(a.reshape(-1).view(np.uint8))
-        self._buf[: src.numel()].copy_(src, non_blocking=non_blocking)
+        env.lib.memcpy_h2d_async(self.ptr, a.ctypes.data, a.nbytes, env.stream())
+        env.lib.stream_synchronize(env.stream())
 
-    def write_from(self, host_tensor, non_blocking=True):
-        """Copy from a (pinned) torch host tensor of bytes."""
-        self._buf[: host_tensor.numel()].copy_(host_tensor, non_blocking=non_blocking)
+    def write_from(self, host, stream=None):
+        """Asynchronous copy from host memory that stays valid until the copy has run: a NumPy array
+        (page-locked, e.g. ``PinnedBuffer.array``, for a truly asynchronous copy) or any object with
+        ``data_ptr()`` / ``numel()`` / ``element_size()`` (a pinned PyTorch CPU tensor)."""
+        env = CudaEnv.instance()
+        env.set_device(self.device_index)
+        src, nbytes = host_pointer(host)
+        env.lib.memcpy_h2d_async(self.ptr, src, min(nbytes, self.nbytes), env.stream() if stream is None else stream)
+
+    def copy_from(self, other, nbytes=None):
+        env = CudaEnv.instance()
+        env.set_device(self.device_index)
+        env.lib.memcpy_d2d_async(self.ptr, other.ptr, self.nbytes if nbytes is None else nbytes, env.stream())
 
     def destroy(self):
-        self._buf = None
-        self.ptr = 0
+        if self.ptr:
+            self._lib.free(self.ptr)
+            self.ptr = 0
+
+    def __del__(self):
+        try:
+            self.destroy()
+        except Exception:
+            pass
+
+
+def host_pointer(host):
+    """(address, bytes) of a contiguous host buffer: NumPy array or an object with ``data_ptr()``."""
+    if hasattr(host, "data_ptr"):
+        return host.data_ptr(), host.numel() * host.element_size()
+    if not host.flags["C_CONTIGUOUS"]:
+        raise ValueError("host buffer must be contiguous")
+    return host.ctypes.data, host.nbytes
 
 
 @BackendDispatcher.instance().register_backend_function("cuda", "allocate_memory")
@@ -216,15 +369,18 @@ def cuda_allocate_memory(device_index, nbytes):
 
 @BackendDispatcher.instance().register_backend_function("cuda", "transfer_memory")
 def cuda_transfer_memory(dst, src):
-    dst._buf[: src.nbytes].copy_(src._buf[: src.nbytes])
+    dst.copy_from(src, src.nbytes)
 
 
 class CudaMemoryView(CudaMemory):
     """A window into another allocation (used for gradient tensors that live inside one flat
-    all-reduce buffer). Keeps the parent buffer alive."""
+    all-reduce buffer). Keeps the parent alive; frees nothing."""
 
-    def __init__(self, torch_bytes_slice, device_index):
+    def __init__(self, parent, offset_bytes, nbytes, device_index):
         self.device_index = device_index
-        self.nbytes = int(torch_bytes_slice.numel())
-        self._buf = torch_bytes_slice
-        self.ptr = torch_bytes_slice.data_ptr()
+        self.nbytes = int(nbytes)
+        self._parent = parent
+        self.ptr = parent.ptr + int(offset_bytes)
+
+    def destroy(self):
+        self.ptr = 0

@@ -111,13 +111,12 @@ def cuda_upload(t, array):
 
 
 def upload_into(t, host):
-    """Asynchronously refill an existing device tensor from host memory (NumPy array, or a torch
-    CPU tensor — pinned for a truly asynchronous copy) holding the logical (NCHW) layout.  The
-    staging buffer of a channels-last tensor is allocated once and reused."""
+    """Asynchronously refill an existing device tensor from host memory holding the logical (NCHW)
+    layout: a NumPy array (page-locked, e.g. ``env.PinnedBuffer(...).array``, for a truly asynchronous
+    copy) or an object with ``data_ptr()`` such as a pinned PyTorch CPU tensor.  The memory must stay
+    valid until the copy has run.  The staging buffer of a channels-last tensor is allocated once and reused."""
     env = _env(t)
-    torch = env.torch
-    src = host if isinstance(host, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(host))
-    src = src.reshape(-1).view(torch.uint8)
+    src = host if hasattr(host, "data_ptr") else np.ascontiguousarray(host)
     if _nontrivial_nhwc(t):
         stage = getattr(t, "_stage", None)
         if stage is None:
@@ -127,6 +126,8 @@ def upload_into(t, host):
         env.lib.nchw_to_nhwc_f32(stage.ptr, _ptr(t), n, c, h, w, env.stream())
     else:
         t._native_array.write_from(src)
+        if not hasattr(host, "data_ptr") and src is not host:
+            env.lib.stream_synchronize(env.stream())  # `src` is a temporary: let the copy finish before it goes away
 
 
 @_reg("cuda", "download")
@@ -535,8 +536,7 @@ def cuda_copy(dst, src):
     if dst.dtype is float32:
         env.lib.copy_f32(_ptr(dst), _ptr(src), _numel(dst.shape), env.stream())
     else:
-        nbytes = dst._native_array.nbytes
-        dst._native_array._buf[:nbytes].copy_(src._native_array._buf[:nbytes])
+        dst._native_array.copy_from(src._native_array, dst._native_array.nbytes)
 
 
 @_reg("cuda", "cast")

@@ -2,9 +2,10 @@
 
 A training step issues a few hundred small launches; at 64 images per GPU the host cannot
 issue them as fast as a B200 retires them.  ``StepGraph`` runs a step function once under
-stream capture (every operator launches on the current stream, allocates from the caching
-allocator's graph pool and never synchronises) and afterwards replays it as a single launch.
-Inputs are static device tensors refilled from host memory before each replay.
+stream capture (every operator launches on the device's compute stream, takes its memory from
+the library's pool, whose blocks are then owned by the graph, and never synchronises) and
+afterwards replays it as a single launch.  Inputs are static device tensors refilled from host
+memory before each replay.
 
 ``InputPrefetcher`` plays the role of the reference's blocking ``x.to(device)`` in its training
 loop (``mytorch/examples/mnist.py:70-88``, ``mytorch/backends/cuda/env.py:553-561``): the next
@@ -19,59 +20,53 @@ import numpy as np
 
 class InputPrefetcher:
     def __init__(self, static_inputs):
-        from mytorch_b200.backends.cuda.env import CudaEnv
+        from mytorch_b200.backends.cuda.env import CudaEnv, CudaMemory
 
         self.env = CudaEnv.instance()
-        torch = self.env.torch
         self.inputs = list(static_inputs)
-        self.copy_stream = torch.cuda.Stream()
+        self.env.set_device(self.inputs[0].device.index)
+        self.copy_stream = self.env.new_stream()
         # two staging slots per input, in the logical (host) layout
-        self.slots = [[self.env.alloc(t._native_array.nbytes, t.device.index) for _ in range(2)] for t in self.inputs]
+        self.slots = [[CudaMemory(t.device.index, t._native_array.nbytes) for _ in range(2)] for t in self.inputs]
         self.copied = [None, None]    # event: slot filled by the copy stream
         self.consumed = [None, None]  # event: slot read by the compute stream
         self.next_slot = 0
         self.staged_slot = None
 
-    def _as_bytes(self, host):
-        torch = self.env.torch
-        src = host if isinstance(host, torch.Tensor) else torch.from_numpy(np.ascontiguousarray(host))
-        return src.reshape(-1).view(torch.uint8)
-
     def stage(self, host_arrays):
-        """Start copying a batch (NumPy arrays or, for truly asynchronous copies, pinned torch CPU
-        tensors, in the logical NCHW layout) into the spare slot.  Returns immediately."""
-        torch = self.env.torch
+        """Start copying a batch (NumPy arrays or pinned host buffers, in the logical NCHW layout; the
+        memory must stay valid until the copy has run, page-locked memory makes it asynchronous) into
+        the spare slot.  Returns immediately."""
+        from mytorch_b200.backends.cuda.env import Event
+
         slot = self.next_slot
-        with torch.cuda.stream(self.copy_stream):
-            if self.consumed[slot] is not None:
-                self.copy_stream.wait_event(self.consumed[slot])
-            for bufs, host in zip(self.slots, host_arrays):
-                src = self._as_bytes(host)
-                bufs[slot][: src.numel()].copy_(src, non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(self.copy_stream)
+        if self.consumed[slot] is not None:
+            self.env.lib.stream_wait_event(self.copy_stream, self.consumed[slot].handle)
+        for bufs, host in zip(self.slots, host_arrays):
+            bufs[slot].write_from(host if hasattr(host, "data_ptr") else np.ascontiguousarray(host), stream=self.copy_stream)
+        ev = Event()
+        ev.record(self.copy_stream)
         self.copied[slot] = ev
         self.staged_slot = slot
         self.next_slot = slot ^ 1
 
     def commit(self):
         """On the compute stream: wait for the staged batch and move it into the static inputs."""
+        from mytorch_b200.backends.cuda.env import Event
         from mytorch_b200.backends.cuda.ops import _nontrivial_nhwc
 
-        torch = self.env.torch
         slot = self.staged_slot
         if slot is None:
             raise RuntimeError("no batch has been staged")
-        stream = torch.cuda.current_stream()
-        stream.wait_event(self.copied[slot])
+        stream = self.env.stream()
+        self.env.lib.stream_wait_event(stream, self.copied[slot].handle)
         for t, bufs in zip(self.inputs, self.slots):
             if _nontrivial_nhwc(t):
                 n, c, h, w = t.shape
-                self.env.lib.nchw_to_nhwc_f32(bufs[slot].data_ptr(), t._native_array.ptr, n, c, h, w, self.env.stream())
+                self.env.lib.nchw_to_nhwc_f32(bufs[slot].ptr, t._native_array.ptr, n, c, h, w, stream)
             else:
-                nbytes = t._native_array.nbytes
-                t._native_array._buf[:nbytes].copy_(bufs[slot][:nbytes], non_blocking=True)
-        ev = torch.cuda.Event()
+                t._native_array.copy_from(bufs[slot], t._native_array.nbytes)
+        ev = Event()
         ev.record(stream)
         self.consumed[slot] = ev
         self.staged_slot = None
@@ -86,13 +81,26 @@ class StepGraph:
         self._prefetcher = None
 
     def capture(self):
-        import torch
+        import ctypes
 
-        torch.cuda.synchronize()
-        self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
+        from mytorch_b200.backends.cuda.env import CudaEnv
+
+        env = CudaEnv.instance()
+        if self.static_inputs:
+            env.set_device(self.static_inputs[0].device.index)
+        stream = env.stream()
+        env.synchronize()
+        env.lib.graph_begin_capture(stream)
+        env._capturing = True
+        try:
             self.result = self.step_fn()
-        torch.cuda.synchronize()
+        finally:
+            env._capturing = False
+            handle = ctypes.c_void_p(0)
+            env.lib.graph_end_capture(stream, ctypes.byref(handle))
+        self.graph = handle.value
+        self._env, self._stream = env, stream
+        env.synchronize()
         return self.result
 
     def load_inputs(self, host_arrays):
@@ -112,5 +120,12 @@ class StepGraph:
             self._prefetcher.commit()
         elif host_arrays is not None:
             self.load_inputs(host_arrays)
-        self.graph.replay()
+        self._env.lib.graph_launch(self.graph, self._stream)
         return self.result
+
+    def destroy(self):
+        """Release the executable graph and the pool blocks only it kept alive."""
+        if self.graph:
+            self._env.synchronize()
+            self._env.lib.graph_destroy(self.graph)
+            self.graph = None

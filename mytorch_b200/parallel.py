@@ -23,6 +23,28 @@ import numpy as np
 from mytorch_b200.tensor import Tensor
 
 
+class _DeviceArray:
+    """Carrier of the CUDA array interface: lets ``torch.as_tensor`` view pool memory without a copy."""
+
+    def __init__(self, ptr, nelems, typestr):
+        self.__cuda_array_interface__ = {"shape": (int(nelems),), "typestr": typestr, "data": (int(ptr), False), "version": 2}
+
+
+def torch_view(memory, nelems, typestr="<f4"):
+    """A PyTorch tensor over a ``CudaMemory`` block (for ``torch.distributed`` only; the block must outlive it)."""
+    import torch
+
+    return torch.as_tensor(_DeviceArray(memory.ptr, nelems, typestr), device=f"cuda:{memory.device_index}")
+
+
+def on_stream(stream_handle, device_index):
+    """Context manager that makes a stream of this library PyTorch's current stream, so that a
+    collective issued inside is ordered after the work already on that stream."""
+    import torch
+
+    return torch.cuda.stream(torch.cuda.ExternalStream(int(stream_handle), device=f"cuda:{device_index}"))
+
+
 def shard_bounds(n, rank, world):
     """Rows [lo, hi) of a batch of ``n`` rows that belong to ``rank`` (near-equal contiguous shards)."""
     base, extra = divmod(n, world)
@@ -47,15 +69,23 @@ class GradBucket:
             off += (n + align_elems - 1) // align_elems * align_elems
         self.sizes = [int(np.prod(p.shape, dtype=np.int64)) for p in self.params]
         self.total = max(off, 1)
-        self.flat = None  # torch tensor (float32), created on first use on the parameters' device
+        self.flat = None      # torch tensor (float32) over the flat buffer, created on first use
+        self.flat_mem = None  # CUDA: the pool block behind it
 
     def _ensure_flat(self):
         if self.flat is None:
             import torch
 
             dev = self.params[0].device
-            where = "cpu" if dev.type == "cpu" else f"cuda:{dev.index if dev.index is not None else torch.cuda.current_device()}"
-            self.flat = torch.zeros(self.total, dtype=torch.float32, device=where)
+            if dev.type == "cpu":
+                self.flat = torch.zeros(self.total, dtype=torch.float32)
+            else:
+                from mytorch_b200.backends.cuda.env import CudaEnv, CudaMemory
+
+                env = CudaEnv.instance()
+                self.flat_mem = CudaMemory(dev.index, 4 * self.total)
+                env.lib.memset_async(self.flat_mem.ptr, 0, 4 * self.total, env.stream())
+                self.flat = torch_view(self.flat_mem, self.total)
         return self.flat
 
     def assign_slots(self):
@@ -63,9 +93,9 @@ class GradBucket:
         backward operators write the parameter's gradient there (``backends/cuda/ops.py``)."""
         from mytorch_b200.backends.cuda.env import CudaMemoryView
 
-        raw = self._ensure_flat().view(dtype=__import__("torch").uint8)
+        self._ensure_flat()
         for p, off, n in zip(self.params, self.offsets, self.sizes):
-            p._grad_slot = CudaMemoryView(raw[4 * off: 4 * (off + n)], p.device.index)
+            p._grad_slot = CudaMemoryView(self.flat_mem, 4 * off, 4 * n, self.flat_mem.device_index)
 
     def pack(self, scale, stream=None):
         """CPU: flat[offset_k : offset_k + n_k] = scale * grad_k for every parameter.  CUDA: the same
@@ -86,7 +116,7 @@ class GradBucket:
             srcs = (ctypes.c_void_p * k)(*[p.grad._native_array.ptr for p, _, _ in stray])
             offs = (ctypes.c_longlong * k)(*[off for _, off, _ in stray])
             sizes = (ctypes.c_longlong * k)(*[n for _, _, n in stray])
-            env.lib.pack_scale_f32(k, srcs, offs, sizes, flat.data_ptr(), float(scale), env.stream() if stream is None else stream)
+            env.lib.pack_scale_f32(k, srcs, offs, sizes, self.flat_mem.ptr, float(scale), env.stream() if stream is None else stream)
         return flat
 
     def point_grads_at_flat(self):
@@ -154,9 +184,9 @@ class DataParallel:
                 from mytorch_b200.autograd import DAGTracker
 
                 if on_cuda:
-                    import torch
+                    from mytorch_b200.backends.cuda.env import CudaEnv
 
-                    self._side = torch.cuda.Stream()
+                    self._side = CudaEnv.instance().new_stream()
                 DAGTracker.instance().leaf_grad_final_hook = self._on_grad_final
             self._reset()
 
@@ -184,18 +214,24 @@ class DataParallel:
             return
         # gradients already sit in the flat buffer; 1/world is an exact scaling for the power-of-two
         # world sizes of one box, so NCCL's average equals the sum of pre-scaled gradients bit for bit
+        from mytorch_b200.backends.cuda.env import CudaEnv, Event
+
+        env = CudaEnv.instance()
+        index = bucket.params[0].device.index
+        env.set_device(index)
         if stream is None:
             flat = bucket.pack(1.0)
-            dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
+            with on_stream(env.stream(), env.current_device()):
+                dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
             return
-        ready = torch.cuda.Event()
-        ready.record(torch.cuda.current_stream())
-        with torch.cuda.stream(stream):
-            stream.wait_event(ready)
-            flat = bucket.pack(1.0, stream=stream.cuda_stream)
+        ready = Event()
+        ready.record(env.stream())
+        env.lib.stream_wait_event(stream, ready.handle)
+        flat = bucket.pack(1.0, stream=stream)
+        with on_stream(stream, env.current_device()):
             dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
-            done = torch.cuda.Event()
-            done.record(stream)
+        done = Event()
+        done.record(stream)
         self._events[b] = done
 
     def _on_grad_final(self, tensor):
@@ -209,15 +245,16 @@ class DataParallel:
     def reduce_gradients(self):
         if self.world == 1:
             return
-        import torch
-
         for b, bucket in enumerate(self.buckets):
             if self._remaining[b] > 0:  # not started by the hook (gradients were set by hand, or no hook)
                 self._launch_bucket(b, self._side)
         if self._side is not None:
+            from mytorch_b200.backends.cuda.env import CudaEnv
+
+            env = CudaEnv.instance()
             for ev in self._events:
                 if ev is not None:
-                    torch.cuda.current_stream().wait_event(ev)
+                    env.lib.stream_wait_event(env.stream(), ev.handle)
         for bucket in self.buckets:
             bucket.point_grads_at_flat()
         self._reset()
@@ -231,7 +268,12 @@ class DataParallel:
 
         for t in list(self.module.parameters()) + list(self.module.buffers()):
             if t.device.type == "cpu":
-                buf = torch.from_numpy(t._numpy())
-            else:
-                buf = t._native_array._buf
-            dist.broadcast(buf, src=src, group=self.group)
+                dist.broadcast(torch.from_numpy(t._numpy()), src=src, group=self.group)
+                continue
+            from mytorch_b200.backends.cuda.env import CudaEnv
+
+            env = CudaEnv.instance()
+            env.set_device(t.device.index)
+            nbytes = t._native_array.nbytes
+            with on_stream(env.stream(), env.current_device()):
+                dist.broadcast(torch_view(t._native_array, nbytes, "|u1"), src=src, group=self.group)

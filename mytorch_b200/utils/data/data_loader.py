@@ -56,10 +56,11 @@ class DataLoader:
 
 class DevicePrefetcher:
     """Iterates a loader of CPU-tensor batches and yields the same batches as CUDA tensors, one batch
-    ahead: while the caller computes on batch k, batch k+1 travels host -> pinned buffer -> device on a
-    side stream; the compute stream only waits for the copy's event (and converts images to the
-    channels-last device layout) when the batch is handed over.  ``dtypes`` optionally casts each
-    element on the host first (labels to int64, as the reference's ``y.to(device, mytorch.int64)``)."""
+    ahead: while the caller computes on batch k, batch k+1 travels host -> page-locked buffer -> device
+    staging buffer on a side stream; the compute stream only waits for the copy's event (and converts
+    images to the channels-last device layout) when the batch is handed over.  Two sets of buffers
+    alternate; a set is refilled only after the compute stream has consumed it.  ``dtypes`` optionally
+    casts each element on the host first (labels to int64, as the reference's ``y.to(device, mytorch.int64)``)."""
 
     def __init__(self, loader, device="cuda:0", dtypes=None):
         self.loader, self.device, self.dtypes = loader, device, dtypes
@@ -68,43 +69,44 @@ class DevicePrefetcher:
         return len(self.loader)
 
     def _stage(self, env, stream, batch, slot):
-        torch = env.torch
+        from mytorch_b200.backends.cuda.env import CudaMemory, Event, PinnedBuffer
+
+        if slot.get("consumed") is not None:
+            slot["consumed"].synchronize()   # host side: the pinned buffers are about to be overwritten
         staged = []
-        with torch.cuda.stream(stream):
-            for k, t in enumerate(batch):
-                a = t._numpy()
-                if self.dtypes is not None and self.dtypes[k] is not None:
-                    a = a.astype(self.dtypes[k].np_dtype, copy=False)
-                a = np.ascontiguousarray(a)
-                key = (k, a.shape, a.dtype.str)
-                pinned = slot.get(key)
-                if pinned is None:
-                    pinned = slot[key] = torch.empty(a.nbytes, dtype=torch.uint8).pin_memory()
-                pinned.numpy()[:] = a.reshape(-1).view(np.uint8)
-                raw = env.alloc(a.nbytes)
-                raw.copy_(pinned, non_blocking=True)
-                raw.record_stream(torch.cuda.current_stream())
-                staged.append((raw, a.shape, a.dtype))
-            event = torch.cuda.Event()
-            event.record(stream)
+        for k, t in enumerate(batch):
+            a = t._numpy()
+            if self.dtypes is not None and self.dtypes[k] is not None:
+                a = a.astype(self.dtypes[k].np_dtype, copy=False)
+            key = (k, a.shape, a.dtype.str)
+            bufs = slot.get(key)
+            if bufs is None:
+                bufs = slot[key] = (PinnedBuffer(a.shape, a.dtype), CudaMemory(None, max(a.nbytes, 1)))
+            pinned, raw = bufs
+            pinned.array[...] = a
+            raw.write_from(pinned.array, stream=stream)
+            staged.append((raw, a.shape, a.dtype))
+        event = Event()
+        event.record(stream)
         return staged, event
 
-    def _hand_over(self, env, staged, event):
+    def _hand_over(self, env, staged, event, slot):
+        from mytorch_b200.backends.cuda.env import Event
         from mytorch_b200.backends.cuda.ops import _nontrivial_nhwc
         from mytorch_b200.dtype import DType
 
-        torch = env.torch
-        torch.cuda.current_stream().wait_event(event)
+        env.lib.stream_wait_event(env.stream(), event.handle)
         out = []
         for raw, shape, np_dtype in staged:
-            raw.record_stream(torch.cuda.current_stream())
             t = Tensor(shape=shape, dtype=DType.from_np_dtype(np_dtype), device=self.device)
             if _nontrivial_nhwc(t):
                 n, c, h, w = shape
-                env.lib.nchw_to_nhwc_f32(raw.data_ptr(), t._native_array.ptr, n, c, h, w, env.stream())
+                env.lib.nchw_to_nhwc_f32(raw.ptr, t._native_array.ptr, n, c, h, w, env.stream())
             else:
-                t._native_array._buf[: raw.numel()].copy_(raw, non_blocking=True)
+                t._native_array.copy_from(raw, t._native_array.nbytes)
             out.append(t)
+        slot["consumed"] = Event()
+        slot["consumed"].record(env.stream())
         return out
 
     def __iter__(self):
@@ -113,17 +115,18 @@ class DevicePrefetcher:
 
         env = CudaEnv.instance()
         env.set_device(Device(self.device).index)
-        stream = env.torch.cuda.Stream()
-        slots = [{}, {}]           # pinned host buffers, two sets: one is being filled while the other is in flight
-        events = [None, None]
+        stream = env.new_stream()
+        slots = [{}, {}]
         pending, k = None, 0
-        for batch in self.loader:
-            if events[k & 1] is not None:
-                events[k & 1].synchronize()   # its pinned buffers are about to be overwritten
-            staged, event = self._stage(env, stream, batch, slots[k & 1])
-            events[k & 1] = event
+        try:
+            for batch in self.loader:
+                slot = slots[k & 1]
+                staged, event = self._stage(env, stream, batch, slot)
+                if pending is not None:
+                    yield self._hand_over(env, *pending)
+                pending, k = (staged, event, slot), k + 1
             if pending is not None:
                 yield self._hand_over(env, *pending)
-            pending, k = (staged, event), k + 1
-        if pending is not None:
-            yield self._hand_over(env, *pending)
+        finally:
+            env.lib.stream_synchronize(stream)
+            env.lib.stream_destroy(stream)

@@ -50,17 +50,18 @@ def test_noalloc_colsum_leaves_free_device_memory_unchanged():
     from mytorch_b200.backends.cuda.env import CudaEnv
 
     env = CudaEnv.instance()
-    torch = env.torch
     rng = np.random.default_rng(7)
     a = rng.standard_normal((20000, 256)).astype(np.float32)
     at, out = g.dev(a), g.dev(np.zeros(256, np.float32))
     call = lambda: env.lib.colsum_noalloc_f32(at._native_array.ptr, 20000, 256, 1.0, out._native_array.ptr, env.stream())
     call()
-    torch.cuda.synchronize()
-    free_before, _ = torch.cuda.mem_get_info()
+    env.synchronize()
+    free_before, _ = env.mem_get_info()
+    pool_before = env.lib.pool_reserved_bytes()
     for _ in range(5):
         call()
-    torch.cuda.synchronize()
-    free_after, _ = torch.cuda.mem_get_info()
+    env.synchronize()
+    free_after, _ = env.mem_get_info()
+    assert env.lib.pool_reserved_bytes() == pool_before
     assert free_after == free_before
     assert rel_err(g.host(out), a.astype(np.float64).sum(axis=0)) < 1e-5
