@@ -265,7 +265,8 @@ __global__ void __launch_bounds__(256) gemm_few_rows_kernel(const float* __restr
 #pragma unroll
   for (int m = 0; m < 16; ++m) acc[m] = 0.f;
   if (col < N) {
-    for (int k = warp; k < K; k += 8) {
+#pragma unroll 8
+    for (int k = warp; k < K; k += 8) {  // unrolled: eight rows' loads are in flight before the first FMA
       const float bv = b[(long long)k * N + col];
       const float* ar = a + (long long)k * M;
 #pragma unroll

@@ -5,6 +5,7 @@
 // gradient to every tied element without re-reading the input.  Backward is a gather over the
 // windows that cover each input element: no atomics, deterministic.
 #include "colreduce.cuh"
+#include <cstdlib>
 
 namespace {
 
@@ -59,6 +60,52 @@ __global__ void __launch_bounds__(256) maxpool_fwd_kernel(const float* __restric
       } else {
 #pragma unroll
         for (int k = 0; k < V; ++k) mask[o + k] = (unsigned short)m[k];
+      }
+    }
+  }
+}
+
+// 2x2 windows with stride 2 that tile the input exactly (no padding, even extents), 4 channels per
+// thread: the four loads of a window are issued back to back with nothing between them but address
+// arithmetic (no bounds tests, 32-bit indices), and every thread works on two windows at once, so eight
+// 16-byte loads are in flight per thread.  Same results as the general kernel above.
+__device__ __forceinline__ void pool2x2_one(float a, float b, float c, float e, float& best, unsigned& m) {
+  best = fmaxf(fmaxf(a, b), fmaxf(c, e));
+  m = (a == best ? 1u : 0u) | (b == best ? 2u : 0u) | (c == best ? 4u : 0u) | (e == best ? 8u : 0u);
+}
+
+__global__ void __launch_bounds__(256) maxpool2x2_fwd_kernel(const float4* __restrict__ x, float4* __restrict__ y, uint2* __restrict__ mask,
+                                                              unsigned C4, unsigned OW, unsigned OH, unsigned total) {
+  const unsigned W_C4 = 2u * OW * C4;  // one input row, in float4 units
+  const unsigned stride = gridDim.x * blockDim.x;
+  for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < total; i0 += 2u * stride) {
+    unsigned idx[2] = {i0, i0 + stride};
+    float4 v[2][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] < total) {
+        const unsigned cg = idx[u] % C4;
+        unsigned t = idx[u] / C4;
+        const unsigned ow = t % OW;
+        t /= OW;  // t = n * OH + oh; the input row is 2 t
+        const unsigned base = (2u * t) * W_C4 + 2u * ow * C4 + cg;
+        v[u][0] = x[base];
+        v[u][1] = x[base + C4];
+        v[u][2] = x[base + W_C4];
+        v[u][3] = x[base + W_C4 + C4];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      if (idx[u] < total) {
+        float4 r;
+        unsigned m0, m1, m2, m3;
+        pool2x2_one(v[u][0].x, v[u][1].x, v[u][2].x, v[u][3].x, r.x, m0);
+        pool2x2_one(v[u][0].y, v[u][1].y, v[u][2].y, v[u][3].y, r.y, m1);
+        pool2x2_one(v[u][0].z, v[u][1].z, v[u][2].z, v[u][3].z, r.z, m2);
+        pool2x2_one(v[u][0].w, v[u][1].w, v[u][2].w, v[u][3].w, r.w, m3);
+        y[idx[u]] = r;
+        if (mask) mask[idx[u]] = make_uint2(m0 | (m1 << 16), m2 | (m3 << 16));
       }
     }
   }
@@ -166,6 +213,14 @@ MTB_API int mtb_max_pool2d_forward_f32(int n, int c, int h, int w, int kh, int k
   int grid = mtb_stream_grid(total, 256);
   cudaStream_t st = (cudaStream_t)stream;
   const bool small = total < (1LL << 31) - (1LL << 26);  // room for the grid-stride overshoot
+  const bool tiles2x2 = kh == 2 && kw == 2 && sh == 2 && sw == 2 && ph == 0 && pw == 0 && h % 2 == 0 && w % 2 == 0;
+  if (vec && tiles2x2 && (long long)n * h * w * (c / 4) < (1LL << 32) - (1LL << 27) && !getenv("MTB_POOL_GENERIC")) {
+    const int g2 = mtb_stream_grid((total + 1) / 2, 256);
+    maxpool2x2_fwd_kernel<<<g2, 256, 0, st>>>((const float4*)x, (float4*)y, (uint2*)tiemask, (unsigned)(c / 4), (unsigned)d.OW, (unsigned)d.OH,
+                                              (unsigned)total);
+    MTB_LAUNCH_CHECK("maxpool2x2_fwd_kernel");
+    return MTB_OK;
+  }
   if (vec && small) maxpool_fwd_kernel<4, unsigned><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
   else if (vec) maxpool_fwd_kernel<4, long long><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);
   else if (small) maxpool_fwd_kernel<1, unsigned><<<grid, 256, 0, st>>>(x, y, tiemask, d, total);

@@ -113,27 +113,40 @@ def test_tensor_api_runs_without_pytorch_being_imported():
     import os
     import subprocess
     import sys
+    import textwrap
 
     from conftest import ROOT
 
-    code = (
-        "import sys, numpy as np\\n"
-        "import mytorch_b200 as mt, mytorch_b200.nn.functional as F\\n"
-        "from mytorch_b200.examples.models import ResNet18Cifar\\n"
-        "from mytorch_b200.optim import SGD\\n"
-        "from mytorch_b200.cuda_graph import StepGraph\\n"
-        "mt.manual_seed(1); net = ResNet18Cifar((16, 16, 32, 32)); net.to('cuda:0')\\n"
-        "opt = SGD(net.parameters(), lr=0.05, momentum=0.9)\\n"
-        "rng = np.random.default_rng(0)\\n"
-        "x = mt.tensor(rng.standard_normal((8, 3, 32, 32)).astype(np.float32), device='cuda:0')\\n"
-        "t = mt.tensor(rng.integers(0, 10, 8).astype(np.int64), device='cuda:0')\\n"
-        "def step():\\n"
-        "    loss = F.cross_entropy(net(x), t); opt.zero_grad(); loss.backward(); opt.step(); return loss\\n"
-        "a = step().item(); step(); g = StepGraph(step, [x, t]); g.capture(); b = g.replay().item()\\n"
-        "assert np.isfinite(a) and np.isfinite(b) and b < a, (a, b)\\n"
-        "assert 'torch' not in sys.modules, 'PyTorch was imported'\\n"
-        "print('ok')\\n"
-    )
+    code = textwrap.dedent("""
+        import sys, numpy as np
+        import mytorch_b200 as mt, mytorch_b200.nn.functional as F
+        from mytorch_b200.examples.models import ResNet18Cifar
+        from mytorch_b200.optim import SGD
+        from mytorch_b200.cuda_graph import StepGraph
+        mt.manual_seed(1)
+        net = ResNet18Cifar((16, 16, 32, 32))
+        net.to('cuda:0')
+        opt = SGD(net.parameters(), lr=0.05, momentum=0.9)
+        rng = np.random.default_rng(0)
+        x = mt.tensor(rng.standard_normal((8, 3, 32, 32)).astype(np.float32), device='cuda:0')
+        t = mt.tensor(rng.integers(0, 10, 8).astype(np.int64), device='cuda:0')
+
+        def step():
+            loss = F.cross_entropy(net(x), t)
+            opt.zero_grad()
+            loss.backward()
+            opt.step()
+            return loss
+
+        a = step().item()
+        step()
+        g = StepGraph(step, [x, t])
+        g.capture()
+        b = g.replay().item()
+        assert np.isfinite(a) and np.isfinite(b) and b < a, (a, b)
+        assert 'torch' not in sys.modules, 'PyTorch was imported'
+        print('ok')
+    """)
     r = subprocess.run([sys.executable, "-c", code], cwd=ROOT, capture_output=True, text=True, timeout=300,
                        env=dict(os.environ, PYTHONPATH=ROOT))
     assert r.returncode == 0 and "ok" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
