@@ -83,9 +83,11 @@ int mtb_graph_destroy(void* graph_exec);
  *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from
  *      mytorch/backends/cuda/ops/conv.py:9-90) ---- */
 long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout);
-/* y[N,OH,OW,Cout] = conv(x[N,H,W,Cin], wt[Cout,KH,KW,Cin]) + bias (bias may be NULL); relu != 0 clamps at 0 */
+/* y[N,OH,OW,Cout] = conv(x[N,H,W,Cin], wt[Cout,KH,KW,Cin]) + bias (bias may be NULL); relu != 0 clamps at 0.
+ * workspace (mtb_conv2d_workspace_bytes(); may be NULL): lets a layer with too few output tiles to fill the
+ * GPU split its reduction across CTAs; the partials are added in a fixed order, results are reproducible. */
 int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                           const float* wt, const float* bias, float* y, int relu, void* stream);
+                           const float* wt, const float* bias, float* y, int relu, void* workspace, long long workspace_bytes, void* stream);
 /* The same forward pass for a convolution whose output feeds a BatchNorm layer: where the kernel family
  * allows, the epilogue also reduces per-channel batch statistics of y from the accumulator rows it
  * already holds, so BatchNorm's own statistics pass (a full re-read of y) can be skipped.  stats: room
@@ -95,7 +97,8 @@ int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh,
  * mytorch/nn/batch_norm.py:123-135; no counterpart in the reference. */
 int mtb_conv2d_stats_max_rows(void);
 int mtb_conv2d_forward_stats_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                                 const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* stream);
+                                 const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* workspace,
+                                 long long workspace_bytes, void* stream);
 /* dx[N,H,W,Cin]: every element is written (zeros where no window reaches); no atomics */
 int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                          const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream);

@@ -67,9 +67,9 @@ _SIGNATURES = {
     "mtb_pack_scale_f32": ([_I, _P, _P, _P, _P, _D, _P], _I),
     "mtb_conv2d_workspace_bytes": (_CONV, _L),
     "mtb_conv2d_plan_f32": (_CONV + [_P], _I),
-    "mtb_conv2d_forward_f32": (_CONV + [_P, _P, _P, _P, _I, _P], _I),
+    "mtb_conv2d_forward_f32": (_CONV + [_P, _P, _P, _P, _I, _P, _L, _P], _I),
     "mtb_conv2d_stats_max_rows": ([], _I),
-    "mtb_conv2d_forward_stats_f32": (_CONV + [_P, _P, _P, _P, _I, _P, _P, _P], _I),
+    "mtb_conv2d_forward_stats_f32": (_CONV + [_P, _P, _P, _P, _I, _P, _P, _P, _L, _P], _I),
     "mtb_batch_norm2d_forward_prestats_f32": ([_I, _I, _I, _I, _P, _P, _P, _D, _D, _P, _P, _P, _P, _P, _I, _P, _I, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_add_f32": (_CONV + [_P, _P, _P, _P, _P, _L, _P], _I),

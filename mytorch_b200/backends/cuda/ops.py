@@ -201,14 +201,16 @@ def cuda_conv2d(input, weight, bias, stride, padding, bn_stats=False):
     n, cin, h, w, kh, kw, sh, sw, ph, pw, cout = a
     oh, ow = (h + 2 * ph - kh) // sh + 1, (w + 2 * pw - kw) // sw + 1
     out = _new((n, cout, oh, ow), input)
+    ws, ws_bytes = env.workspace(env.lib.conv2d_workspace_bytes(*a))
     if bn_stats:
         partials = CudaMemory(input.device.index, env.lib.conv2d_stats_max_rows() * 3 * cout * 4)
         rows = ctypes.c_int(0)
-        env.lib.conv2d_forward_stats_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, partials.ptr, ctypes.byref(rows), env.stream())
+        env.lib.conv2d_forward_stats_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, partials.ptr, ctypes.byref(rows), ws, ws_bytes,
+                                         env.stream())
         if rows.value > 0:
             out._bn_partials = (partials, rows.value)
         return out
-    env.lib.conv2d_forward_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, env.stream())
+    env.lib.conv2d_forward_f32(*a, _ptr(x), _ptr(wt), _ptr(bias), _ptr(out), 0, ws, ws_bytes, env.stream())
     return out
 
 

@@ -10,10 +10,13 @@ MTB_API long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int k
   return a > b ? a : b;
 }
 
+// workspace (may be NULL): scratch of mtb_conv2d_workspace_bytes(); with it, layers whose output has too few
+// tiles to fill the GPU split their reduction across CTAs (partials in the workspace, added in a fixed order).
 MTB_API int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                                   const float* wt, const float* bias, float* y, int relu, void* stream) {
+                                   const float* wt, const float* bias, float* y, int relu, void* workspace, long long workspace_bytes,
+                                   void* stream) {
   if (mtb_tc_conv2d_forward_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, y))
-    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
+    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, workspace, workspace_bytes, stream);
   return mtb_conv2d_forward_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
 }
 
@@ -26,11 +29,13 @@ MTB_API int mtb_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw,
 MTB_API int mtb_conv2d_stats_max_rows() { return 4 * mtb_sm_count(); }
 
 MTB_API int mtb_conv2d_forward_stats_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                                         const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* stream) {
+                                         const float* wt, const float* bias, float* y, int relu, float* stats, int* stats_rows, void* workspace,
+                                         long long workspace_bytes, void* stream) {
   MTB_REQUIRE(stats && stats_rows, "conv2d_forward_stats: stats buffer and row counter are required");
   *stats_rows = 0;
   if (mtb_tc_conv2d_forward_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, y))
-    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream, stats, stats_rows);
+    return mtb_tc_conv2d_forward_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, workspace, workspace_bytes, stream, stats,
+                                     stats_rows);
   return mtb_conv2d_forward_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, x, wt, bias, y, relu, stream);
 }
 

@@ -18,8 +18,8 @@ long long mtb_tc_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, in
 bool mtb_tc_conv2d_forward_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
                                      const float* wt, const float* y);
 int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                              const float* wt, const float* bias, float* y, int relu, void* stream, float* stats = nullptr,
-                              int* stats_rows = nullptr);
+                              const float* wt, const float* bias, float* y, int relu, void* workspace, long long workspace_bytes, void* stream,
+                              float* stats = nullptr, int* stats_rows = nullptr);
 bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                                    const float* wt, const float* dx);
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,

@@ -122,7 +122,17 @@ struct GemmParams {
   // (count, mean, M2) over the output rows this CTA produced (the grid is a multiple of n_tiles, so a
   // CTA always works on the same column tile)
   float* stats;
+  // Split reduction (splits > 1): unit u = tile * splits + split works on reduction blocks
+  // [split * kb_per_split, ...); every unit writes its raw accumulator to partial[u] and draws a ticket for
+  // its tile; the unit that draws the last ticket adds the partials in split order and finishes the tile.
+  int splits, kb_per_split;
+  float* partial;
 };
+
+// One ticket counter per output tile of a split launch; back to zero when the launch ends.  Launches that
+// split must not overlap on one GPU (they share the counters), which holds for work on one stream.
+constexpr int kMaxSplitTiles = 1024;
+static __device__ unsigned int g_gemm_tickets[kMaxSplitTiles];
 
 // A stage holds kKB reduction blocks of 32 (each one 128-byte swizzle span per operand row).  One
 // producer/consumer hand-over costs the issuing thread 300-400 cycles that do not overlap with MMA
@@ -148,6 +158,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   __shared__ uint64_t bar_full[8], bar_empty[8], bar_tfull[2], bar_tempty[2];
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int split_last;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -173,7 +184,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = tmem_slot;
-  const int tiles = p.m_tiles * p.n_tiles;
+  const int S = p.splits;
+  const int tiles = p.m_tiles * p.n_tiles * S;  // work units: (tile, split) pairs, the splits of a tile adjacent
   volatile int* abort_ptr = &abort_flag;
 
   if (warp == 0) {
@@ -184,7 +196,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+      for (int unit = blockIdx.x; unit < tiles && ok; unit += gridDim.x) {
+        const int tile = unit / S, split = unit - tile * S;
+        const int kb0 = split * p.kb_per_split;
+        const int kb1 = kb0 + p.kb_per_split < p.num_kb ? kb0 + p.kb_per_split : p.num_kb;
         const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
         int pix_w = 0, pix_h = 0, pix_n = 0;
         if (AMODE == A_IM2COL) {
@@ -194,9 +209,9 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           pix_n = t / p.OH;
         }
         // reduction blocks in (tap, channel-block) order; plain GEMMs have a single "tap"
-        int kh = 0, kw = 0, cc = 0;
-        for (int kb = 0; kb < p.num_kb && ok; kb += C::kKB) {
-          const int nblk = p.num_kb - kb < C::kKB ? p.num_kb - kb : C::kKB;  // the last stage may hold one block
+        int cc = kb0 % p.cchunks, kw = (kb0 / p.cchunks) % p.KW, kh = (kb0 / p.cchunks) / p.KW;
+        for (int kb = kb0; kb < kb1 && ok; kb += C::kKB) {
+          const int nblk = kb1 - kb < C::kKB ? kb1 - kb : C::kKB;  // the last stage may hold one block
           if (!mbar_wait(smem_u32(&bar_empty[stage]), phase ^ 1u, abort_ptr, 1)) { ok = false; break; }
           const uint32_t full = smem_u32(&bar_full[stage]);
           mbar_expect_tx(full, (uint32_t)nblk * (C::kABytes + C::kBBytes));
@@ -246,7 +261,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     uint32_t phase = 0;
     int t = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+    for (int unit = blockIdx.x; unit < tiles && ok; unit += gridDim.x, ++t) {
+      const int split = unit % S;
+      const int kb0 = split * p.kb_per_split;
+      const int kb1 = kb0 + p.kb_per_split < p.num_kb ? kb0 + p.kb_per_split : p.num_kb;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
       ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 2));
@@ -254,12 +272,12 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * BN;
       uint32_t acc = 0;
-      for (int kb = 0; kb < p.num_kb; kb += C::kKB) {
+      for (int kb = kb0; kb < kb1; kb += C::kKB) {
         ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_full[stage]), phase, abort_ptr, 3));
         if (!ok) break;
         tc_fence_after();
         const uint32_t a_lo = a_lo0 + stage * (C::kStageBytes >> 4), b_lo = b_lo0 + stage * (C::kStageBytes >> 4);
-        const bool second = C::kKB == 2 && kb + 1 < p.num_kb;
+        const bool second = C::kKB == 2 && kb + 1 < kb1;
         if (elect_one()) {
           mma_tf32_words(d_tmem, a_lo, a_hi, b_lo, b_hi, idesc, acc);
           mma_tf32_words(d_tmem, a_lo + a_step, a_hi, b_lo + b_step, b_hi, idesc, 1u);
@@ -291,7 +309,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     WarpColStats<(STATS && !LANE_SUMS) ? BN / 32 : 1> stats;
     LaneColSums<LANE_SUMS ? BN / 32 : 1> sums;
     if constexpr (LANE_SUMS) sums.reset(); else stats.reset();
-    for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++t) {
+    for (int unit = blockIdx.x; unit < tiles; unit += gridDim.x, ++t) {
+      const int tile = unit / S;
       const int m0 = (tile / p.n_tiles) * 128, n0 = (tile % p.n_tiles) * BN;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
@@ -308,17 +327,14 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
         orow_index = ((long long)nn * p.o_H + p.o_h0 + p.o_sh * i) * p.o_W + p.o_w0 + p.o_sw * j;
       }
       float* orow = p.out + orow_index * p.ldo;
-      if constexpr (STATS) {
-        // the forward convolution that feeds a BatchNorm layer: full column tiles (N % 32 == 0, checked on
-        // the host), vector stores, and the per-channel statistics of what is stored
-        const bool valid = row < p.M;
-        const float cnt = (float)__popc(__ballot_sync(0xffffffffu, valid));
-#pragma unroll
-        for (int c0 = 0; c0 < BN; c0 += 32) {
-          uint32_t r[32];
-          tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-          tmem_ld_wait();
-          const int col0 = n0 + c0;
+      const bool valid = row < p.M;
+      const float cnt = STATS ? (float)__popc(__ballot_sync(0xffffffffu, valid)) : 0.f;
+      // r: this lane's row of the finished accumulator, columns c0 .. c0+31 of the tile
+      auto finish = [&](int c0, const uint32_t (&r)[32]) {
+        const int col0 = n0 + c0;
+        if constexpr (STATS) {
+          // the forward convolution that feeds a BatchNorm layer: full column tiles (N % 32 == 0, checked on
+          // the host), vector stores, and the per-channel statistics of what is stored
           if (col0 < p.N) {  // warp-uniform
             float o[32];
 #pragma unroll
@@ -333,52 +349,127 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
               if (cnt > 0.f) stats.add_chunk(c0 / 32, o, valid, cnt, lane);
             }
           }
-        }
-        if constexpr (LANE_SUMS) sums.cnt += valid ? 1.f : 0.f; else stats.n += cnt;
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
-        continue;
-      }
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
-        tmem_ld_wait();
-        const int col0 = n0 + c0;
-        if (row < p.M && col0 < p.N) {
-          if (vec_ok && col0 + 32 <= p.N) {
+        } else {
+          if (valid && col0 < p.N) {
+            if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
-              float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (p.bias) {
-                const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+              for (int j = 0; j < 32; j += 4) {
+                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                if (p.bias) {
+                  const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
+                  v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+                }
+                if (p.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
+                *reinterpret_cast<float4*>(orow + col0 + j) = v;
               }
-              if (p.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
-              *reinterpret_cast<float4*>(orow + col0 + j) = v;
-            }
-          } else {
+            } else {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              if (col0 + j < p.N) {
-                float v = __uint_as_float(r[j]);
-                if (p.bias) v += p.bias[col0 + j];
-                if (p.relu) v = fmaxf(v, 0.f);
-                orow[col0 + j] = v;
+              for (int j = 0; j < 32; ++j) {
+                if (col0 + j < p.N) {
+                  float v = __uint_as_float(r[j]);
+                  if (p.bias) v += p.bias[col0 + j];
+                  if (p.relu) v = fmaxf(v, 0.f);
+                  orow[col0 + j] = v;
+                }
               }
             }
           }
         }
+      };
+      auto release_accumulator = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+      };
+      auto count_rows = [&]() {
+        if constexpr (LANE_SUMS) sums.cnt += valid ? 1.f : 0.f;
+        else if constexpr (STATS) stats.n += cnt;
+      };
+      if (S == 1) {
+        if constexpr (STATS) {
+#pragma unroll
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+            tmem_ld_wait();
+            finish(c0, r);
+          }
+        } else {
+#pragma unroll 1
+          for (int c0 = 0; c0 < BN; c0 += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c0), r);
+            tmem_ld_wait();
+            finish(c0, r);
+          }
+        }
+        count_rows();
+        release_accumulator();
+        continue;
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+      // Split reduction.  partial[unit][chunk][quarter][j][lane]: a warp stores 128 contiguous bytes per column.
+      constexpr int kChunks = BN / 32;
+      float* part = p.partial + (((long long)unit * kChunks) * 4 + quarter) * 1024 + lane;
+#pragma unroll 1
+      for (int c = 0; c < kChunks; ++c) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN + c * 32), r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; ++j) part[c * 4096 + j * 32] = __uint_as_float(r[j]);
+      }
+      release_accumulator();
+      __threadfence();
+      asm volatile("bar.sync 1, 128;" ::: "memory");  // the four epilogue warps
+      if (threadIdx.x == 64) {
+        const unsigned int ticket = atomicAdd(&g_gemm_tickets[tile], 1u);
+        split_last = (ticket == (unsigned int)S - 1u);
+        if (split_last) g_gemm_tickets[tile] = 0u;  // every unit of the tile has drawn: ready for the next launch
+      }
+      asm volatile("bar.sync 1, 128;" ::: "memory");
+      if (!split_last) continue;
+      __threadfence();
+      const float* first = p.partial + (((long long)tile * S * kChunks) * 4 + quarter) * 1024 + lane;
+      auto reduce_chunk = [&](int c, uint32_t (&r)[32]) {
+        float acc[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc[j] = __ldcg(first + c * 4096 + j * 32);
+        for (int sp = 1; sp < S; ++sp) {  // fixed order: split 0, 1, 2, ...
+          const float* q = first + (long long)sp * kChunks * 4096 + c * 4096;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) acc[j] += __ldcg(q + j * 32);
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(acc[j]);
+      };
+      if constexpr (STATS) {
+#pragma unroll
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t r[32];
+          reduce_chunk(c, r);
+          finish(c * 32, r);
+        }
+      } else {
+#pragma unroll 1
+        for (int c = 0; c < kChunks; ++c) {
+          uint32_t r[32];
+          reduce_chunk(c, r);
+          finish(c * 32, r);
+        }
+      }
+      count_rows();
+      if constexpr (STATS) {
+        // which unit of a tile comes last differs from run to run, so the statistics of a split tile go to
+        // a row chosen by the tile, not by the CTA: results stay bit-reproducible
+        float* row = p.stats + ((long long)(tile / p.n_tiles) * 4 + quarter) * 3 * p.N;
+        if constexpr (LANE_SUMS) { sums.store(row, p.N, n0, p.N, p.bias, lane); sums.reset(); }
+        else { stats.store(row, p.N, n0, p.N, lane); stats.reset(); }
+      }
     }
-    if constexpr (STATS) {
+    if (STATS && S == 1) {
       float* row = p.stats + ((long long)(blockIdx.x / p.n_tiles) * 4 + quarter) * 3 * p.N;
       if constexpr (LANE_SUMS) sums.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, p.bias, lane);
-      else stats.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, lane);
+      else if constexpr (STATS) stats.store(row, p.N, (blockIdx.x % p.n_tiles) * BN, p.N, lane);
     }
   }
 
@@ -401,9 +492,9 @@ int launch_tc(const CUtensorMap& mapA, const CUtensorMap& mapB, const GemmParams
   auto kernel = tc_gemm_kernel<BN, AMODE, BMODE, STATS>;
   static unsigned long long configured = 0;
   if (int rc = mtb_opt_in_smem((const void*)kernel, (int)C::kSmemBytes, &configured)) return rc;
-  int tiles = p.m_tiles * p.n_tiles;
+  int tiles = p.m_tiles * p.n_tiles * p.splits;  // work units
   int grid = tiles < mtb_sm_count() ? tiles : mtb_sm_count();
-  if (STATS) grid = grid / p.n_tiles * p.n_tiles;  // every CTA stays on one column tile (see GemmParams::stats)
+  if (STATS && p.splits == 1) grid = grid / p.n_tiles * p.n_tiles;  // every CTA stays on one column tile (see GemmParams::stats)
   kernel<<<grid, 192, C::kSmemBytes, st>>>(mapA, mapB, p);
   MTB_LAUNCH_CHECK("tc_gemm_kernel");
   return MTB_OK;
@@ -433,6 +524,48 @@ int pick_bn_for(int n, long long rows) {
   int bn = pick_bn(n);
   while (bn > 64 && m_tiles * ((n + bn - 1) / bn) < want) bn >>= 1;
   return bn;
+}
+
+// Tile width and reduction split for the im2col / GEMM kernel.  These kernels are bound by what one SM
+// can pull from L2 into shared memory (about 89 GB/s: 47 B per cycle), then by the MMA rate, so a launch
+// is priced as waves x reduction blocks per unit x the slower of (bytes of one block of A and B at that
+// rate, four MMAs), plus, for a split reduction, the last unit's pass over the partials.  The cheapest
+// (tile width, splits) wins; a split is only considered when all its units fit the GPU at once
+// (tiles x splits <= SMs) and every unit keeps at least eight reduction blocks.
+struct GemmPlan { int bn, splits, kb_per_split; };
+
+GemmPlan plan_gemm(int n, long long rows, int num_kb, bool may_split, int force_bn = 0) {
+  const int sms = mtb_sm_count();
+  const long long m_tiles = (rows + 127) / 128;
+  static const int kSplits[] = {1, 2, 3, 4, 6, 8};
+  GemmPlan best{force_bn ? force_bn : pick_bn_for(n, rows), 1, num_kb};
+  // Measured: the split only pays when even 64-wide tiles leave half the GPU idle (the 4x4 layers at 64
+  // images: 41 -> 24 us for the data gradient of 512 -> 512); with more tiles than that the last unit's pass
+  // over the partials costs more than the idle SMs did (256 -> 256 on 8x8 at 64 images: 20 -> 40 us).
+  if (m_tiles * ((n + 63) / 64) > sms / 2 || num_kb < 64) may_split = false;  // short reductions gain nothing either
+  if (!may_split || getenv("MTB_DISABLE_SPLITK")) return best;
+  double best_ns = 1e30;
+  for (int bn = force_bn ? force_bn : pick_bn(n); bn >= (force_bn ? force_bn : 64); bn >>= 1) {
+    const long long tiles = m_tiles * ((n + bn - 1) / bn);
+    for (int want : kSplits) {
+      if (want > 1 && (tiles * want > sms || num_kb / want < 8 || tiles > kMaxSplitTiles)) continue;
+      const int per = (num_kb + want - 1) / want;
+      const int splits = (num_kb + per - 1) / per;
+      const long long waves = (tiles * splits + sms - 1) / sms;
+      const double load_ns = (16384.0 + bn * 128.0) / 89.0;
+      const double mma_ns = 4.0 * (bn == 64 ? 48.0 : bn == 128 ? 64.0 : 128.0) / 1.9;
+      double ns = (double)waves * per * (load_ns > mma_ns ? load_ns : mma_ns) + 2000.0;
+      if (splits > 1) ns += splits * 128.0 * bn * 4.0 / 150.0 + 1500.0;
+      if (ns < best_ns) { best_ns = ns; best = GemmPlan{bn, splits, per}; }
+    }
+  }
+  return best;
+}
+
+long long split_partial_bytes(const GemmPlan& g, long long rows, int n) {
+  if (g.splits <= 1) return 0;
+  const long long tiles = ((rows + 127) / 128) * ((n + g.bn - 1) / g.bn);
+  return tiles * g.splits * 128LL * g.bn * 4;
 }
 
 bool al16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
@@ -522,6 +655,7 @@ int mtb_tc_gemm_f32(int m, int n, int k, const float* a, int trans_a, const floa
   else rc = tc::encode_tiled_2d(&mapB, b, k, n, n, 32, 32, true);
   if (rc) return rc;
   GemmParams p{};
+  p.splits = 1; p.kb_per_split = (k + 31) / 32;
   p.M = m; p.N = n; p.num_kb = (k + 31) / 32;
   p.m_tiles = (m + 127) / 128; p.n_tiles = (n + bn - 1) / bn;
   p.out = c; p.ldo = n; p.bias = bias; p.relu = relu;
@@ -547,10 +681,14 @@ bool mtb_tc_conv2d_forward_supported(int n, int cin, int h, int w, int kh, int k
 // rows [rows][3][cout] of per-channel (count, mean, M2) of y and *stats_rows receives their number;
 // *stats_rows == 0 means this launch did not produce statistics.
 int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,
-                              const float* wt, const float* bias, float* y, int relu, void* stream, float* stats, int* stats_rows) {
+                              const float* wt, const float* bias, float* y, int relu, void* workspace, long long workspace_bytes, void* stream,
+                              float* stats, int* stats_rows) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
   const long long M = (long long)n * oh * ow, K = (long long)kh * kw * cin;
-  const int bn = pick_bn_for(cout, M);
+  const bool rows_path = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, cin, cout, pick_bn_for(cout, M)).ok;
+  GemmPlan gp = plan_gemm(cout, M, (int)(K / 32), !rows_path && workspace != nullptr);
+  if (split_partial_bytes(gp, M, cout) > workspace_bytes) gp = GemmPlan{pick_bn_for(cout, M), 1, (int)(K / 32)};
+  const int bn = rows_path ? pick_bn_for(cout, M) : gp.bn;
   if (stats_rows) *stats_rows = 0;
   const bool want_stats = stats && stats_rows && !relu && cout % 32 == 0 && (!bias || al16(bias)) && !getenv("MTB_DISABLE_CONV_STATS");
   CUtensorMap mapA, mapB;
@@ -569,10 +707,11 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
   p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cout + bn - 1) / bn;
   p.out = y; p.ldo = cout; p.bias = bias; p.relu = relu;
   p.OW = ow; p.OH = oh; p.SW = sw; p.SH = sh; p.PW = pw; p.PH = ph; p.KW = kw; p.KH = kh; p.cchunks = cin / 32;
+  p.splits = gp.splits; p.kb_per_split = gp.kb_per_split; p.partial = (float*)workspace;
   // short reductions (1x1 shortcuts) leave the epilogue no main loop to hide the statistics behind
-  if (want_stats && p.num_kb >= 16 && p.m_tiles * p.n_tiles >= p.n_tiles) {
+  if (want_stats && p.num_kb >= 16) {
     p.stats = stats;
-    *stats_rows = stats_rows_for(p.m_tiles * p.n_tiles, p.n_tiles);
+    *stats_rows = gp.splits > 1 ? p.m_tiles * 4 : stats_rows_for(p.m_tiles * p.n_tiles, p.n_tiles);
     cudaStream_t st = (cudaStream_t)stream;
     if (bn == 64) return launch_tc<64, A_IM2COL, B_KMAJOR, true>(mapA, mapB, p, st);
     if (bn == 128) return launch_tc<128, A_IM2COL, B_KMAJOR, true>(mapA, mapB, p, st);
@@ -604,9 +743,14 @@ bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw,
 // addend (may be NULL): dx = dgrad + addend.  Fused into the epilogue on the row-staged path; the
 // other paths write dgrad and add afterwards.
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
-                            const float* wt, const float* addend, float* dx, void*, long long, void* stream) {
+                            const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream) {
   const int oh = (h + 2 * ph - kh) / sh + 1, ow = (w + 2 * pw - kw) / sw + 1;
-  const int bn = pick_bn_for(cin, (long long)n * h * w / (sh * sw));
+  // one tile width for all residue classes (the weight tensor map is shared): the one the cost model picks
+  // for a class-sized problem
+  const long long class_rows = (long long)n * h * w / (sh * sw);
+  const bool rows_path = row_conv_plan(n, h, w, kh, kw, sh, sw, ph, pw, cout, cin, pick_bn_for(cin, class_rows)).ok;
+  const int class_kb = ((kh + sh - 1) / sh) * ((kw + sw - 1) / sw) * (cout / 32);
+  const int bn = rows_path ? pick_bn_for(cin, class_rows) : plan_gemm(cin, class_rows, class_kb, workspace != nullptr).bn;
   cudaStream_t st = (cudaStream_t)stream;
   CUtensorMap mapB;
   int rc = tc::encode_tiled_2d(&mapB, wt, cout, (long long)kh * kw * cin, (long long)kh * kw * cin, 32, 32, true);
@@ -647,6 +791,9 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
       GemmParams p{};
       const long long M = (long long)n * ah.count * aw.count;
       p.M = (int)M; p.N = cin; p.num_kb = ah.taps * aw.taps * (cout / 32);
+      GemmPlan gp = plan_gemm(cin, M, p.num_kb, workspace != nullptr, bn);
+      if (split_partial_bytes(gp, M, cin) > workspace_bytes) gp = GemmPlan{bn, 1, p.num_kb};
+      p.splits = gp.splits; p.kb_per_split = gp.kb_per_split; p.partial = (float*)workspace;
       p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
       p.out = dx; p.ldo = cin; p.bias = nullptr; p.relu = 0;
       p.OW = aw.count; p.OH = ah.count; p.SW = 1; p.SH = 1; p.PW = -aw.lower; p.PH = -ah.lower; p.KW = aw.taps; p.KH = ah.taps;
@@ -1005,6 +1152,9 @@ long long mtb_tc_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, in
   if (cin % 32) return 0;
   WgradPlan q = wgrad_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
   long long bytes = (long long)q.splits * q.Kw * cout * 4 + 256;
+  // forward / data gradient with a split reduction: at most one unit per SM, each a 128 x 256 fp32 partial
+  const long long split_bytes = (long long)mtb_sm_count() * 128 * 256 * 4;
+  if (split_bytes > bytes) bytes = split_bytes;
   const WgradRowsPlan rq = wgrad_rows_plan(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout);
   if (rq.ok) {
     const long long b2 = (long long)rq.splits * q.Kw * cout * 4 + 256;

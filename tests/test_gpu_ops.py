@@ -131,19 +131,27 @@ def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
     assert np.array_equal(g.host(pt), prev)
 
 
-def test_conv_is_deterministic(g):
+@pytest.mark.parametrize("shape", [(8, 64, 16, 16), (8, 256, 8, 8), (16, 512, 4, 4)])
+def test_conv_is_deterministic(g, shape):
+    """Bitwise-equal results on repeated runs, also for the layers whose forward pass and data gradient
+    split their reduction across CTAs (few output tiles: 8x8 and 4x4 images) and whose BatchNorm
+    statistics come from the convolution's epilogue."""
+    n, c, h, w = shape
     rng = np.random.default_rng(5)
-    x = rng.standard_normal((8, 64, 16, 16)).astype(np.float32)
-    w = rng.standard_normal((64, 64, 3, 3)).astype(np.float32)
-    dy = rng.standard_normal((8, 64, 16, 16)).astype(np.float32)
+    x = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    wt = rng.standard_normal((c, c, 3, 3)).astype(np.float32)
+    dy = rng.standard_normal((n, c, h, w)).astype(np.float32)
+    gamma, beta = np.ones(c, np.float32), np.zeros(c, np.float32)
     outs = []
-    for _ in range(2):
-        xt, wt = g.dev(x, True), g.dev(w, True)
-        y = g.op("conv2d")(xt, wt, None, (1, 1), (1, 1))
-        dx, dw, _ = g.op("conv2d_backward")(g.dev(dy), xt, wt, None, (1, 1), (1, 1))
-        outs.append((g.host(y), g.host(dx), g.host(dw)))
-    for a, b in zip(*outs):
-        assert np.array_equal(a, b)
+    for _ in range(3):
+        xt, wtt = g.dev(x, True), g.dev(wt, True)
+        y = g.op("conv2d")(xt, wtt, None, (1, 1), (1, 1), bn_stats=True)
+        _, mean, var = g.op("batch_norm2d")(y, g.dev(gamma), g.dev(beta), 1e-5, True, 0.1, None, None)
+        dx, dw, _ = g.op("conv2d_backward")(g.dev(dy), xt, wtt, None, (1, 1), (1, 1))
+        outs.append((g.host(y), g.host(dx), g.host(dw), g.host(mean), g.host(var)))
+    for other in outs[1:]:
+        for a, b in zip(outs[0], other):
+            assert np.array_equal(a, b)
 
 
 def test_linear(g):
