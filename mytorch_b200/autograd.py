@@ -39,6 +39,13 @@ class DAGTracker:
         # optional callback(tensor): a leaf tensor has received its last gradient contribution of
         # the running backward pass (used to start gradient all-reduces while backward continues)
         self.leaf_grad_final_hook = None
+        # optional callback(): a backend that ran gradient kernels beside the main chain (weight gradients
+        # on a second CUDA stream) makes them visible to it; called before a gradient is read or handed
+        # out during the pass, and when the pass ends
+        self.join_hook = None
+        # operators whose backward may be told ``defer_weight_gradient=True``: the returned parameter
+        # gradient then becomes valid at the next join_hook() call, not when the backward returns
+        self.deferrable = set()
         # operator name -> index of the input whose already accumulated gradient the operator's
         # backward can add itself (keyword ``accumulate_dx``); the tape then stores the returned
         # gradient instead of launching an add
@@ -101,10 +108,12 @@ class DAGTracker:
                 cand = node.inputs[slot]
                 if isinstance(cand, Tensor) and cand.requires_grad and cand.grad is not None:
                     fused = cand
+            extra = {}
             if fused is not None:
-                grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs, accumulate_dx=fused.grad))
-            else:
-                grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs))
+                extra["accumulate_dx"] = fused.grad
+            if node.name in self.deferrable and self.join_hook is not None:
+                extra["defer_weight_gradient"] = True
+            grads = list(func(*[t.grad for t in node.outputs], *node.helpers, *node.inputs, **extra))
             grads += [None] * (len(node.inputs) - len(grads))
             for arg, grad in zip(node.inputs, grads):
                 if arg is None or not isinstance(arg, Tensor) or not arg.requires_grad:
@@ -115,11 +124,18 @@ class DAGTracker:
                     else:
                         if arg.grad.shape != grad.shape:
                             raise MismatchShapesError([arg.grad.shape, grad.shape])
+                        if self.join_hook is not None and arg._grad_node is None:  # a leaf: its gradient may come from there
+                            self.join_hook()
                         arg.grad = arg.grad + grad
                 if hook is not None and id(arg) in pending:
                     pending[id(arg)] -= 1
                     if pending[id(arg)] == 0 and arg.grad is not None:
+                        if self.join_hook is not None:
+                            self.join_hook()
                         hook(arg)
+
+        if self.join_hook is not None:
+            self.join_hook()
 
         for node in order:
             for t in node.outputs:

@@ -243,6 +243,15 @@ class CudaEnv:
         self._scratch = {}
         self._retired_scratch = []
         self._capturing = False
+        # weight gradients run beside the rest of backward on a second stream (see fork_side / join_side)
+        self._side_streams = {}
+        self._side_scratch = {}
+        self._side_keepalive = []
+        self._side_busy = set()
+        self.overlap_weight_gradients = not os.environ.get("MTB_SERIAL_WGRAD")
+        from mytorch_b200.autograd import DAGTracker
+
+        DAGTracker.instance().join_hook = self.join_side
 
     # ---- devices, streams
     def current_device(self):
@@ -283,19 +292,57 @@ class CudaEnv:
         self.lib.tc_status(ctypes.byref(out))
         return out.value
 
+    # ---- a second stream for work nothing on the compute stream waits for until backward ends
+    def fork_side(self, keepalive=()):
+        """The side stream of the current device, ordered after everything enqueued on the compute
+        stream so far.  ``keepalive``: objects whose device memory the side-stream work reads or writes;
+        they are held until ``join_side`` so that the pool cannot hand their blocks to compute-stream
+        work while the side stream still uses them."""
+        dev = self.current_device()
+        side = self._side_streams.get(dev)
+        if side is None:
+            side = self._side_streams[dev] = self.lib.stream_create()
+        ev = Event()
+        ev.record(self.stream())
+        self.lib.stream_wait_event(side, ev.handle)
+        self._side_keepalive.extend(keepalive)
+        self._side_busy.add(dev)
+        return side
+
+    def join_side(self):
+        """Make the compute stream of every device wait for its side stream; release the kept objects."""
+        if not self._side_busy:
+            return
+        current = self.current_device()
+        for dev in list(self._side_busy):
+            self.set_device(dev)
+            ev = Event()
+            ev.record(self._side_streams[dev])
+            self.lib.stream_wait_event(self.stream(), ev.handle)
+        self.set_device(current)
+        self._side_busy.clear()
+        self._side_keepalive.clear()
+
+    def side_workspace(self, nbytes):
+        """Scratch for side-stream kernels (the compute stream's scratch may be in use at the same time)."""
+        return self._grow_scratch(self._side_scratch, nbytes)
+
     # ---- memory
     def workspace(self, nbytes):
         """Scratch for kernels that need it (split-K partials, per-CTA reduction partials).
         One buffer per device, shared by all operators: they run in order on one stream."""
+        return self._grow_scratch(self._scratch, nbytes)
+
+    def _grow_scratch(self, table, nbytes):
         dev = self.current_device()
-        buf = self._scratch.get(dev)
+        buf = table.get(dev)
         if buf is None or buf.nbytes < nbytes:
             if buf is not None:
                 # a captured graph may hold this block's address: it is kept for the life of the
                 # process so that the pool can never hand it to a tensor a replay would overwrite
                 self._retired_scratch.append(buf)
             buf = CudaMemory(dev, max(int(nbytes), 1 << 20))
-            self._scratch[dev] = buf
+            table[dev] = buf
         return buf.ptr, buf.nbytes
 
 
@@ -313,6 +360,7 @@ class CudaMemory:
 
     def read(self, shape, np_dtype):
         env = CudaEnv.instance()
+        env.join_side()  # a host read must see what the side stream has produced, too
         env.set_device(self.device_index)
         out = np.empty(shape, dtype=np_dtype)
         env.lib.memcpy_d2h_async(out.ctypes.data, self.ptr, out.nbytes, env.stream())

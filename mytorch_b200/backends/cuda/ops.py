@@ -215,10 +215,12 @@ def cuda_conv2d(input, weight, bias, stride, padding, bn_stats=False):
 
 
 @_reg("cuda", "conv2d_backward")
-def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None):
+def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None, defer_weight_gradient=False):
     """``accumulate_dx``: a gradient the input has already received from another consumer; when given,
     the returned dx is the data gradient PLUS that tensor (added in the convolution's epilogue where
-    the kernel allows), and the caller stores it instead of adding the two itself."""
+    the kernel allows), and the caller stores it instead of adding the two itself.
+    ``defer_weight_gradient``: the caller (the tape) does not need dw until it calls ``CudaEnv.join_side``;
+    the weight gradient then runs on the device's side stream, beside whatever the caller enqueues next."""
     _f32(output_grad, input, weight)
     env = _env(input)
     want_dx, want_dw, cin = input.requires_grad, weight.requires_grad, input.shape[1]
@@ -247,13 +249,24 @@ def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accu
             if accumulate_dx is not None:
                 dx = BackendDispatcher.instance().dispatch("cuda", "add")(dx, accumulate_dx, 1)
     if want_dw:
+        # Nothing in the rest of backward reads this layer's weight gradient, so it runs on the side
+        # stream, beside the data-gradient / BatchNorm chain that the next layer waits for, and is
+        # joined when backward ends (or before anything touches the gradient: see DAGTracker.backward).
+        # A weight that already holds a gradient (shared weights) accumulates on the compute stream.
+        wst, wws, wws_bytes = st, ws, ws_bytes
+        if defer_weight_gradient and env.overlap_weight_gradients and weight.grad is None:
+            wst = env.fork_side((x, output_grad))
+            wws, wws_bytes = env.side_workspace(env.lib.conv2d_workspace_bytes(*a))
         if padded:
             wide = _new((weight.shape[0], _TC_CHANNELS) + tuple(weight.shape[2:]), weight)
-            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(wide), ws, ws_bytes, st)
-            dw = _take_channels(env, wide, cin, weight, out=_grad_buffer(weight))
+            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(wide), wws, wws_bytes, wst)
+            dw = _grad_buffer(weight)
+            env.lib.resize_channels_f32(_ptr(wide), _ptr(dw), weight.shape[0] * weight.shape[2] * weight.shape[3], _TC_CHANNELS, cin, wst)
+            if wst is not st:
+                env._side_keepalive.append(wide)
         else:
             dw = _grad_buffer(weight)
-            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(dw), ws, ws_bytes, st)
+            env.lib.conv2d_wgrad_f32(*a, _ptr(x), _ptr(output_grad), _ptr(dw), wws, wws_bytes, wst)
     if bias is not None and bias.requires_grad:
         db = _colsum(env, output_grad, _numel(output_grad.shape) // a[-1], a[-1], bias, out=_grad_buffer(bias))
     return [dx, dw, db]

@@ -23,15 +23,20 @@ def conv2d(input: Tensor, weight: Tensor, bias=None, stride=1, padding=0, bn_sta
 
 
 @tracker.register_backward_function("conv2d")
-def conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None):
+def conv2d_backward(output_grad, input, weight, bias, stride, padding, accumulate_dx=None, defer_weight_gradient=False):
     """``accumulate_dx`` is the gradient ``input`` already holds (the tape passes it for operators
-    listed in ``DAGTracker.fused_accumulate``): the returned dx then includes it."""
+    listed in ``DAGTracker.fused_accumulate``): the returned dx then includes it.
+    ``defer_weight_gradient`` (passed by the tape for operators in ``DAGTracker.deferrable``): the backend
+    may compute dw beside the rest of the pass; it is complete after the tape's next ``join_hook()``."""
     backend = dispatch(input.device, "conv2d_backward")
+    extra = {}
     if accumulate_dx is not None:
-        dx, dw, db = backend(output_grad, input, weight, bias, stride, padding, accumulate_dx=accumulate_dx)
-    else:
-        dx, dw, db = backend(output_grad, input, weight, bias, stride, padding)
+        extra["accumulate_dx"] = accumulate_dx
+    if defer_weight_gradient and input.device.type == "cuda":
+        extra["defer_weight_gradient"] = True
+    dx, dw, db = backend(output_grad, input, weight, bias, stride, padding, **extra)
     return [dx, dw, db]
 
 
 tracker.fused_accumulate["conv2d"] = 0  # input 0's accumulated gradient can be folded into the backward
+tracker.deferrable.add("conv2d")        # the weight gradient may run beside the rest of backward

@@ -88,6 +88,7 @@ class LayerwiseChecker:
     # ---- backward: wraps every registered backward function
     def _backward(self, name, func):
         def wrapped(*args, **kwargs):
+            kwargs.pop("defer_weight_gradient", None)  # every gradient is inspected right after its operator returns
             grads = func(*args, **kwargs)
             g = [_h(t) if t is not None and hasattr(t, "shape") else None for t in grads]
             if name == "conv2d":
