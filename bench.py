@@ -330,6 +330,24 @@ def kernel_legs(env, peaks):
     out["config1_conv56_dgrad_tflops"] = flops1 / t_d / 1e12
     out["config1_conv56_wgrad_tflops"] = flops1 / t_w / 1e12
     del c1
+    # a late layer: 256->256 3x3 on 8x8 at the full batch (im2col-mode kernels; 33.5 MB per tensor, five sets rotate past L2)
+    late = []
+    for _ in range(5):
+        late.append((mt.tensor(rng.standard_normal((n, 256, 8, 8)).astype(np.float32), device="cuda", requires_grad=True),
+                     mt.tensor(rng.standard_normal((n, 256, 8, 8)).astype(np.float32), device="cuda")))
+    w256 = mt.tensor((rng.standard_normal((256, 256, 3, 3)) / 48).astype(np.float32), device="cuda", requires_grad=True)
+    flops256 = 2.0 * n * 8 * 8 * 256 * 256 * 9
+    t_f = timed(lambda i: op("conv2d")(late[i % 5][0], w256, None, (1, 1), (1, 1)))
+    w256.requires_grad = False
+    t_d = timed(lambda i: op("conv2d_backward")(late[i % 5][1], late[i % 5][0], w256, None, (1, 1), (1, 1)))
+    w256.requires_grad = True
+    for xx, _ in late:
+        xx.requires_grad = False
+    t_w = timed(lambda i: op("conv2d_backward")(late[i % 5][1], late[i % 5][0], w256, None, (1, 1), (1, 1)))
+    out["conv3x3_256_8x8_fwd_tflops"] = flops256 / t_f / 1e12
+    out["conv3x3_256_8x8_dgrad_tflops"] = flops256 / t_d / 1e12
+    out["conv3x3_256_8x8_wgrad_tflops"] = flops256 / t_w / 1e12
+    del late, w256
     # configs[2]: BatchNorm2d(128) -> ReLU -> MaxPool2d(2,2) on 256x128x56x56 (S = 411 MB >> L2), forward and backward
     big2 = (0.5 + 2.0 * rng.standard_normal((64, 128, 56, 56))).astype(np.float32)
     x2 = mt.tensor(np.concatenate([big2] * 4, axis=0), device="cuda", requires_grad=True)
@@ -366,6 +384,49 @@ def kernel_legs(env, peaks):
     out["hbm_frac"] = {k: out[k] / peaks["hbm_gbs"] for k in out if k.endswith("_gbs")}
     out["tf32_frac"] = {k: out[k] / tf32_peak for k in out if k.endswith("_tflops")}
     return roof, out
+
+
+def profile_leg(env, name, iters=3):
+    """One operator at a benchmark shape, a few launches, nothing else on the device: the command
+    profiled with ncu for the summaries under profiles/ (kept small so that a full-counter capture ends
+    by itself).  conv64: 64->64 3x3 on 512x32x32 forward, forward with BatchNorm statistics, dgrad,
+    wgrad; wgrad256: weight gradient of 256->256 3x3 on 512x8x8 (im2col kernel); pool: 2x2/2 max-pool
+    forward and backward on 256x128x56x56; bn64: BatchNorm forward / backward on 512x64x32x32."""
+    import mytorch_b200 as mt
+    from mytorch_b200.backends.backend_dispatcher import BackendDispatcher
+
+    op = lambda n: BackendDispatcher.instance().dispatch("cuda", n)
+    rng = np.random.default_rng(2)
+    dev = lambda a, grad=False: mt.tensor(a.astype(np.float32), device="cuda", requires_grad=grad)
+    if name in ("conv64", "bn64"):
+        x, dy = dev(rng.standard_normal((512, 64, 32, 32)), True), dev(rng.standard_normal((512, 64, 32, 32)))
+        if name == "conv64":
+            w = dev(rng.standard_normal((64, 64, 3, 3)) / 24, True)
+            for _ in range(iters):
+                op("conv2d")(x, w, None, (1, 1), (1, 1))
+                op("conv2d")(x, w, None, (1, 1), (1, 1), bn_stats=True)
+                op("conv2d_backward")(dy, x, w, None, (1, 1), (1, 1))
+        else:
+            g, b = dev(np.ones(64), True), dev(np.zeros(64), True)
+            for _ in range(iters):
+                y, m, v = op("batch_norm2d")(x, g, b, 1e-5, True, 0.1, None, None)
+                op("batch_norm2d_backward")(dy, m, v, x, g, b, 1e-5)
+    elif name == "wgrad256":
+        x, dy = dev(rng.standard_normal((512, 256, 8, 8))), dev(rng.standard_normal((512, 256, 8, 8)))
+        w = dev(rng.standard_normal((256, 256, 3, 3)) / 48, True)
+        for _ in range(iters):
+            op("conv2d_backward")(dy, x, w, None, (1, 1), (1, 1))
+    elif name == "pool":
+        x = dev(np.concatenate([rng.standard_normal((64, 128, 56, 56)).astype(np.float32)] * 4, axis=0))
+        dy = dev(rng.standard_normal((256, 128, 28, 28)))
+        for _ in range(iters):
+            y = op("max_pool2d")(x, (2, 2), (2, 2), (0, 0))
+            op("max_pool2d_backward")(dy, y, x, (2, 2), (2, 2), (0, 0))
+    else:
+        sys.exit(f"unknown leg {name}")
+    env.synchronize()
+    status = env.tensor_core_status()
+    print(json.dumps({"leg": name, "iterations": iters, "tensor_core_status": status}))
 
 
 def run_gpu_arm(args):
@@ -584,12 +645,18 @@ def main():
                     help="gradient all-reduce buckets (N>1): 1 = one all-reduce after backward, more = start each "
                          "bucket on a side stream as soon as backward has finished its gradients")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
+    ap.add_argument("--leg", default=None, choices=["conv64", "wgrad256", "pool", "bn64"],
+                    help="run one operator at a benchmark shape for a few launches and exit (the small command profiled with ncu)")
     ap.add_argument("--only-legs", action="store_true",
                     help="run only the single-kernel legs (conv fwd/dgrad/wgrad, BatchNorm, ReLU) and print their JSON; "
                          "this is the command profiled with ncu for the summaries under profiles/")
     args = ap.parse_args()
     GLOBAL_BATCH = args.global_batch
-    if args.only_legs:
+    if args.leg:
+        from mytorch_b200.backends.cuda.env import CudaEnv
+
+        profile_leg(CudaEnv.instance(), args.leg)
+    elif args.only_legs:
         from mytorch_b200.backends.cuda.env import CudaEnv
 
         roof, kernels = kernel_legs(CudaEnv.instance(), measured_peaks())
