@@ -130,9 +130,7 @@ class DAGTracker:
                 if hook is not None and id(arg) in pending:
                     pending[id(arg)] -= 1
                     if pending[id(arg)] == 0 and arg.grad is not None:
-                        if self.join_hook is not None:
-                            self.join_hook()
-                        hook(arg)
+                        hook(arg)  # the gradient may still be in flight on the backend's side stream: the hook orders itself after it
 
         if self.join_hook is not None:
             self.join_hook()

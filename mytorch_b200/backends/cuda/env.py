@@ -309,6 +309,17 @@ class CudaEnv:
         self._side_busy.add(dev)
         return side
 
+    def side_event(self):
+        """An event after everything enqueued so far on the current device's side stream (None if idle):
+        a third stream that consumes side-stream results (the gradient all-reduce) waits on it directly,
+        without making the compute stream wait."""
+        dev = self.current_device()
+        if dev not in self._side_busy:
+            return None
+        ev = Event()
+        ev.record(self._side_streams[dev])
+        return ev
+
     def join_side(self):
         """Make the compute stream of every device wait for its side stream; release the kept objects."""
         if not self._side_busy:

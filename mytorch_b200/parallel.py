@@ -227,6 +227,9 @@ class DataParallel:
         ready = Event()
         ready.record(env.stream())
         env.lib.stream_wait_event(stream, ready.handle)
+        weight_gradients = env.side_event()  # weight gradients run on the compute stream's side stream
+        if weight_gradients is not None:
+            env.lib.stream_wait_event(stream, weight_gradients.handle)
         flat = bucket.pack(1.0, stream=stream)
         with on_stream(stream, env.current_device()):
             dist.all_reduce(flat, op=dist.ReduceOp.AVG, group=self.group)
