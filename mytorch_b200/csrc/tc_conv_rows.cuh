@@ -47,6 +47,8 @@ struct RowConvParams {
 
 constexpr uint32_t kRowLead = 1024;  // room for the left-most tap of the first position to reach back
 constexpr int kRowAStages = 2;
+constexpr int kRowIssuers = 2;                        // warps 1..2 issue MMAs, on alternating tiles
+constexpr int kRowThreads = 32 * (1 + kRowIssuers + 4);  // producer, issuers, four epilogue warps
 
 // Why a weight stage holds several taps: one producer/consumer hand-over through a pair of
 // mbarriers costs the issuing thread about 300-400 cycles that do not overlap with tensor-core
@@ -56,14 +58,34 @@ constexpr int kRowAStages = 2;
 // MT = tiles of 128 positions per work item.  With streamed weights two tiles share every weight
 // stage (two accumulators), which halves the L2 -> shared-memory weight traffic per MMA; that traffic,
 // at ~47 B/cycle/SM, is what bounds the 128-channel layers.
+// A ring slot is consumed by whichever issuing warp owns the tile, and a parity wait cannot tell "lap L not
+// yet filled" from "lap L + 1 filled".  So the warp that has seen lap L of a slot filled publishes L + 1 in
+// shared memory, and nobody starts waiting for lap L + 1 before that (bounded like every other wait).
+__device__ __forceinline__ bool lap_wait(volatile int* seen, int lap, volatile int* abort_flag, int code) {
+  if (*seen >= lap) return true;
+  const long long start = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (*seen >= lap) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - start > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(&g_tc_status[0], 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 template <int BN, int BMODE, int FK, int MT, bool STATS>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kRowThreads, 1)
 tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const RowConvParams p) {
   constexpr uint32_t kTapBytes = BN * 128;
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_afull[kRowAStages], bar_aempty[kRowAStages], bar_bfull[8], bar_bempty[8], bar_tfull[2], bar_tempty[2], bar_bres;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
+  __shared__ int seen_a[kRowAStages], seen_b[8];  // laps of each ring slot an issuing warp has seen filled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -92,6 +114,8 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     }
     mbar_init(smem_u32(&bar_bres), 1);
     abort_flag = 0;
+    for (int s = 0; s < kRowAStages; ++s) seen_a[s] = 0;
+    for (int s = 0; s < 8; ++s) seen_b[s] = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -170,8 +194,8 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------------------------------------ MMA issuer
+  } else if (warp <= kRowIssuers) {
+    // ------------------------------------------------------------ MMA issuers
     // The whole warp runs the loops converged and one elected lane issues: with warp-uniform
     // control flow the descriptors stay in uniform registers, which roughly halves the cost of
     // issuing a tcgen05.mma compared with a lane-0 branch around everything.
@@ -182,12 +206,21 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     constexpr uint32_t tap_step = kTapBytes >> 4;
     const uint32_t b_lo0 = BMODE == B_MNMAJOR ? desc_lo_mnmajor(b_base) : desc_lo_kmajor(b_base);
     const uint32_t row_step = (uint32_t)p.Wp * 8u;  // one image row, in 16-byte units (a pixel is 128 B)
-    int as = 0, bs = 0;
-    uint32_t aphase = 0, bphase = 0;
-    int t = 0;
+    // Two warps issue, each every other tile of this CTA into its own accumulator buffer.  What one warp does
+    // between tiles (waiting for the accumulator and the next activation stage, position arithmetic, commits)
+    // then runs while the other warp's MMAs keep the tensor pipe busy.  The two never accumulate into the same
+    // buffer, so the interleaving of their MMAs in the pipe does not change any sum.  The rings are consumed in
+    // tile order, so a warp finds its place in them from the tile's ordinal alone.
+    const int iw = warp - 1;
+    const int b_per_cc = p.resident ? 0 : (FK == 3 ? 3 : (taps + p.tps - 1) / p.tps);
     bool ok = true;
     if (p.resident && blockIdx.x < tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bres), 0, abort_ptr, 17));
-    for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++t) {
+    for (int t = iw; ok; t += kRowIssuers) {
+      const int tile = blockIdx.x + t * (int)gridDim.x;
+      if (tile >= tiles) break;
+      const int a_g = t * p.cchunks, b_g = a_g * b_per_cc;
+      int as = a_g % kRowAStages, bs = b_g % BST;
+      int alap = a_g / kRowAStages, blap = b_g / BST;
       const int col = ((tile / p.n_tiles) * (128 * MT)) % p.Wp;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
@@ -197,8 +230,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       const uint32_t d_tmem = tmem_base + buf * (MT * BN);
       constexpr uint32_t tile_step = 128u * 8u;  // the next tile's positions start 128 pixels (of 8 units) further
       for (int cc = 0; cc < p.cchunks && ok; ++cc) {
-        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_afull[as]), aphase, abort_ptr, 14));
+        ok = __all_sync(0xffffffffu, lap_wait(&seen_a[as], alap, abort_ptr, 18) &&
+                                         mbar_wait(smem_u32(&bar_afull[as]), (uint32_t)alap & 1u, abort_ptr, 14));
         if (!ok) break;
+        *(volatile int*)&seen_a[as] = alap + 1;
         tc_fence_after();
         // position q0 of this tile sits PH rows and `col` pixels into the staged rows; tap
         // (kh, kw) reads (kh - PH) rows and (kw - PW) pixels away from it
@@ -237,8 +272,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           // streamed weights, 3x3 filter: one filter row (3 taps) per weight stage, straight-line issue
 #pragma unroll
           for (int kh = 0; kh < 3; ++kh) {
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), bphase, abort_ptr, 15));
+            ok = __all_sync(0xffffffffu, lap_wait(&seen_b[bs], blap, abort_ptr, 19) &&
+                                             mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
             if (!ok) break;
+            *(volatile int*)&seen_b[bs] = blap + 1;
             tc_fence_after();
             const uint32_t b_row = b_lo0 + bs * (b_stage_bytes >> 4);
             if (elect_one()) {
@@ -253,7 +290,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               mma_commit(smem_u32(&bar_bempty[bs]));
             }
             __syncwarp();
-            if (++bs == BST) { bs = 0; bphase ^= 1u; }
+            if (++bs == BST) { bs = 0; ++blap; }
           }
           if (ok && elect_one()) mma_commit(smem_u32(&bar_aempty[as]));
           __syncwarp();
@@ -261,8 +298,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           int kh = 0, kw = 0;
           for (int tap0 = 0; tap0 < taps && ok; tap0 += p.tps) {
             const int cnt = taps - tap0 < p.tps ? taps - tap0 : p.tps;
-            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), bphase, abort_ptr, 15));
+            ok = __all_sync(0xffffffffu, lap_wait(&seen_b[bs], blap, abort_ptr, 19) &&
+                                             mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
             if (!ok) break;
+            *(volatile int*)&seen_b[bs] = blap + 1;
             tc_fence_after();
             if (elect_one()) {
               uint32_t b_lo = b_lo0 + bs * (b_stage_bytes >> 4);
@@ -283,18 +322,18 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
             __syncwarp();
             kw += cnt;
             while (kw >= p.KW) { kw -= p.KW; ++kh; }
-            if (++bs == BST) { bs = 0; bphase ^= 1u; }
+            if (++bs == BST) { bs = 0; ++blap; }
           }
           if (ok && elect_one()) mma_commit(smem_u32(&bar_aempty[as]));
           __syncwarp();
         }
-        if (++as == kRowAStages) { as = 0; aphase ^= 1u; }
+        if (++as == kRowAStages) { as = 0; ++alap; }
       }
       if (ok && elect_one()) mma_commit(smem_u32(&bar_tfull[buf]));
       __syncwarp();
     }
   } else {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+    // ------------------------------------------------------------ epilogue (the last four warps)
     const int quarter = warp & 3;
     int t = 0;
     const bool vec_ok = (p.ldo % 4 == 0) &&
@@ -504,7 +543,7 @@ int launch_row_conv_kernel(const CUtensorMap& mapA, const CUtensorMap& mapB, con
   const int items = ((p.m_tiles + MT - 1) / MT) * p.n_tiles;
   int grid = items < mtb_sm_count() ? items : mtb_sm_count();
   if (STATS) grid = grid / p.n_tiles * p.n_tiles;  // every CTA stays on one output-channel tile
-  kernel<<<grid, 192, smem_bytes, st>>>(mapA, mapB, p);
+  kernel<<<grid, kRowThreads, smem_bytes, st>>>(mapA, mapB, p);
   MTB_LAUNCH_CHECK("tc_conv_rows_kernel");
   return MTB_OK;
 }
