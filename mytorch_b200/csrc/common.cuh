@@ -21,6 +21,14 @@ int mtb_sm_count();
 // per device, so `done_mask` (one per kernel, zero-initialised) remembers the ordinals already set.
 int mtb_opt_in_smem(const void* kernel, int bytes, unsigned long long* done_mask);
 
+// Lanes: up to three auxiliary streams per device for an entry point that enqueues several launches which
+// do not depend on one another (and each fill only part of the GPU).  mtb_fork_lanes makes lanes 1..n-1 wait
+// for everything enqueued on `main` so far and returns their streams (lane 0 is `main` itself);
+// mtb_join_lanes makes `main` wait for them.  Inside a stream capture both become graph dependencies.
+constexpr int kMaxLanes = 4;
+int mtb_fork_lanes(cudaStream_t main, int lanes, cudaStream_t* out);
+int mtb_join_lanes(cudaStream_t main, int lanes);
+
 #define MTB_REQUIRE(cond, ...) \
   do { if (!(cond)) return mtb_fail(MTB_ERR_INVALID, __VA_ARGS__); } while (0)
 

@@ -35,6 +35,49 @@ int mtb_opt_in_smem(const void* kernel, int bytes, unsigned long long* done_mask
   return MTB_OK;
 }
 
+namespace {
+struct Lanes {
+  cudaStream_t stream[kMaxLanes - 1];
+  cudaEvent_t fork, join[kMaxLanes - 1];
+  bool made;
+};
+Lanes g_lanes[64];
+}  // namespace
+
+int mtb_fork_lanes(cudaStream_t main, int lanes, cudaStream_t* out) {
+  int dev = 0;
+  MTB_CUDA(cudaGetDevice(&dev));
+  MTB_REQUIRE(dev >= 0 && dev < 64 && lanes >= 1 && lanes <= kMaxLanes, "mtb_fork_lanes: device %d, %d lanes", dev, lanes);
+  Lanes& l = g_lanes[dev];
+  if (!l.made) {
+    for (int i = 0; i < kMaxLanes - 1; ++i) {
+      MTB_CUDA(cudaStreamCreateWithFlags(&l.stream[i], cudaStreamNonBlocking));
+      MTB_CUDA(cudaEventCreateWithFlags(&l.join[i], cudaEventDisableTiming));
+    }
+    MTB_CUDA(cudaEventCreateWithFlags(&l.fork, cudaEventDisableTiming));
+    l.made = true;
+  }
+  out[0] = main;
+  if (lanes > 1) MTB_CUDA(cudaEventRecord(l.fork, main));
+  for (int i = 1; i < lanes; ++i) {
+    MTB_CUDA(cudaStreamWaitEvent(l.stream[i - 1], l.fork, 0));
+    out[i] = l.stream[i - 1];
+  }
+  return MTB_OK;
+}
+
+int mtb_join_lanes(cudaStream_t main, int lanes) {
+  int dev = 0;
+  MTB_CUDA(cudaGetDevice(&dev));
+  MTB_REQUIRE(dev >= 0 && dev < 64 && g_lanes[dev].made, "mtb_join_lanes without mtb_fork_lanes");
+  Lanes& l = g_lanes[dev];
+  for (int i = 1; i < lanes; ++i) {
+    MTB_CUDA(cudaEventRecord(l.join[i - 1], l.stream[i - 1]));
+    MTB_CUDA(cudaStreamWaitEvent(main, l.join[i - 1], 0));
+  }
+  return MTB_OK;
+}
+
 MTB_API const char* mtb_last_error() { return g_last_error; }
 
 MTB_API int mtb_version() { return 1; }

@@ -781,17 +781,33 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
       if (ah.count > 0 && aw.count > 0 && (ah.taps == 0 || aw.taps == 0)) need_zero = true;
     }
   if (need_zero) MTB_CUDA(cudaMemsetAsync(dx, 0, (size_t)n * h * w * cin * 4, st));
+  // The classes write disjoint pixels.  When one class fills only part of the GPU they run side by side on
+  // separate lanes (then without split reductions, whose tickets and partials one launch at a time owns).
+  int live = 0;
+  for (int a = 0; a < sh; ++a)
+    for (int b = 0; b < sw; ++b) {
+      Axis ah = axis(a, h, oh, kh, sh, ph), aw = axis(b, w, ow, kw, sw, pw);
+      if (ah.count > 0 && aw.count > 0 && ah.taps > 0 && aw.taps > 0) ++live;
+    }
+  const long long class_units = ((class_rows + 127) / 128) * ((cin + bn - 1) / bn);
+  const bool side_by_side = live > 1 && class_units < mtb_sm_count() && !getenv("MTB_DGRAD_SERIAL");
+  const int lanes = side_by_side ? (live < kMaxLanes ? live : kMaxLanes) : 1;
+  cudaStream_t lane_stream[kMaxLanes];
+  rc = mtb_fork_lanes(st, lanes, lane_stream);
+  if (rc) return rc;
+  int launched = 0;
   for (int a = 0; a < sh; ++a) {
     for (int b = 0; b < sw; ++b) {
       Axis ah = axis(a, h, oh, kh, sh, ph), aw = axis(b, w, ow, kw, sw, pw);
       if (ah.count == 0 || aw.count == 0 || ah.taps == 0 || aw.taps == 0) continue;
+      cudaStream_t cst = lane_stream[launched++ % lanes];
       CUtensorMap mapA;
       rc = tc::encode_im2col_4d(&mapA, dy, n, oh, ow, cout, aw.lower, ah.lower, aw.upper, ah.upper, 1, 1, 32, 128);
       if (rc) return rc;
       GemmParams p{};
       const long long M = (long long)n * ah.count * aw.count;
       p.M = (int)M; p.N = cin; p.num_kb = ah.taps * aw.taps * (cout / 32);
-      GemmPlan gp = plan_gemm(cin, M, p.num_kb, workspace != nullptr, bn);
+      GemmPlan gp = plan_gemm(cin, M, p.num_kb, workspace != nullptr && lanes == 1, bn);
       if (split_partial_bytes(gp, M, cin) > workspace_bytes) gp = GemmPlan{bn, 1, p.num_kb};
       p.splits = gp.splits; p.kb_per_split = gp.kb_per_split; p.partial = (float*)workspace;
       p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
@@ -805,10 +821,12 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
           p.b_tap_x[jh * aw.taps + jw] = (fkh * kw + fkw) * cin;
         }
       p.o_strided = 1; p.o_Hc = ah.count; p.o_Wc = aw.count; p.o_H = h; p.o_W = w; p.o_h0 = ah.start; p.o_w0 = aw.start; p.o_sh = sh; p.o_sw = sw;
-      rc = launch_tc_bn<A_IM2COL, B_MNMAJOR>(bn, mapA, mapB, p, st);
+      rc = launch_tc_bn<A_IM2COL, B_MNMAJOR>(bn, mapA, mapB, p, cst);
       if (rc) return rc;
     }
   }
+  rc = mtb_join_lanes(st, lanes);
+  if (rc) return rc;
   if (addend) return mtb_add_f32(dx, addend, dx, (long long)n * h * w * cin, 1.0f, st);
   return MTB_OK;
 }
