@@ -42,23 +42,30 @@ __global__ void __launch_bounds__(256) sgd_kernel(float* p, const float* g, floa
 }
 
 constexpr int kMaxTensors = 96;
+constexpr int kSgdChunk = 4096;  // elements per CTA: four float4 per thread and array in flight
 struct SgdTable {
   float* p[kMaxTensors];
   const float* g[kMaxTensors];
   float* buf[kMaxTensors];
   long long n[kMaxTensors];
   int first[kMaxTensors];
+  int chunk_start[kMaxTensors + 1];  // CTA b works on tensor k with chunk_start[k] <= b < chunk_start[k + 1]
   int count;
 };
 
-// blockIdx.y selects the tensor; blockIdx.x strides over its elements.
+// One CTA per chunk of kSgdChunk elements of one tensor (a model has a few large tensors and dozens of
+// tiny ones: a grid of tensors x the largest tensor's chunks would be mostly empty CTAs).
 __global__ void __launch_bounds__(256) sgd_multi_kernel(const __grid_constant__ SgdTable t, SgdHyper h) {
-  int k = blockIdx.y;
-  if (k >= t.count) return;
-  long long n = t.n[k];
-  long long tid = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  int lo = 0, hi = t.count - 1;
+  while (lo < hi) {  // last k with chunk_start[k] <= blockIdx.x
+    const int mid = (lo + hi + 1) >> 1;
+    if (t.chunk_start[mid] <= (int)blockIdx.x) lo = mid; else hi = mid - 1;
+  }
+  const int k = lo;
+  const long long e0 = (long long)((int)blockIdx.x - t.chunk_start[k]) * kSgdChunk;
+  const long long left = t.n[k] - e0;
   h.first = t.first[k];
-  sgd_span(t.p[k], t.g[k], t.buf[k], n, h, tid, (long long)gridDim.x * blockDim.x);
+  sgd_span(t.p[k] + e0, t.g[k] + e0, t.buf[k] + e0, left < kSgdChunk ? left : kSgdChunk, h, threadIdx.x, blockDim.x);
 }
 
 // Gather `count` gradient tensors into one flat buffer, scaling on the way.
@@ -101,7 +108,7 @@ MTB_API int mtb_sgd_multi_f32(int count, float* const* params, const float* cons
   for (int base = 0; base < count; base += kMaxTensors) {
     SgdTable t;
     t.count = count - base < kMaxTensors ? count - base : kMaxTensors;
-    long long maxn = 1;
+    long long chunks = 0;
     for (int k = 0; k < t.count; ++k) {
       MTB_REQUIRE(sizes[base + k] >= 0 && params[base + k] && grads[base + k] && momentum_buffers[base + k], "sgd_multi: null tensor %d", base + k);
       t.p[k] = params[base + k];
@@ -109,12 +116,13 @@ MTB_API int mtb_sgd_multi_f32(int count, float* const* params, const float* cons
       t.buf[k] = momentum_buffers[base + k];
       t.n[k] = sizes[base + k];
       t.first[k] = is_first[base + k];
-      if (t.n[k] > maxn) maxn = t.n[k];
+      t.chunk_start[k] = (int)chunks;
+      chunks += (t.n[k] + kSgdChunk - 1) / kSgdChunk;
+      MTB_REQUIRE(chunks < (1LL << 30), "sgd_multi: too many elements in one call");
     }
-    int gx = mtb_div_up((maxn + 3) / 4, 256);
-    int cap = mtb_sm_count() * 8;
-    if (gx > cap) gx = cap;
-    dim3 grid(gx, t.count);
+    t.chunk_start[t.count] = (int)chunks;
+    if (chunks == 0) continue;
+    dim3 grid((unsigned int)chunks);
     sgd_multi_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(t, h);
     MTB_LAUNCH_CHECK("sgd_multi_kernel");
   }

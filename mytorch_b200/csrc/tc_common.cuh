@@ -68,6 +68,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_limit(bar, parity, abort_flag, code, kWaitCycles);
 }
 
+// 32-byte store (sm_100): a lane that owns a run of eight floats writes whole sectors
+__device__ __forceinline__ void st_global_v8(float* p, float a, float b, float c, float d, float e, float f, float g, float h) {
+  asm volatile("st.global.v8.f32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(p), "f"(a), "f"(b), "f"(c), "f"(d), "f"(e), "f"(f), "f"(g), "f"(h)
+               : "memory");
+}
+
+// eight consecutive floats of a row: one 32-byte store where the row allows it (wide), else two 16-byte ones
+__device__ __forceinline__ void st_row8(float* p, float4 a, float4 b, bool wide) {
+  if (wide) {
+    st_global_v8(p, a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w);
+  } else {
+    *reinterpret_cast<float4*>(p) = a;
+    *reinterpret_cast<float4*>(p + 4) = b;
+  }
+}
+
 // ---- TMA loads (global -> shared, completion on an mbarrier) ----
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

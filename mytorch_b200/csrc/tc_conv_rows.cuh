@@ -39,6 +39,7 @@ struct RowConvParams {
   const float* bias;
   const float* addend;     // optional [same shape as out]: out = conv + addend (gradient accumulation)
   int relu;
+  int issuers;             // issuing warps at work (1 or 2)
   int b_tap_x[64];         // MN-major B only: first column of tap j in the weight matrix
   // STATS kernels only: partial rows [(blockIdx.x / n_tiles) * 4 + epilogue warp][3][N] of per-channel
   // (count, mean, M2) over the pixels this CTA produced (grid is a multiple of n_tiles)
@@ -215,7 +216,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     const int b_per_cc = p.resident ? 0 : (FK == 3 ? 3 : (taps + p.tps - 1) / p.tps);
     bool ok = true;
     if (p.resident && blockIdx.x < tiles) ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bres), 0, abort_ptr, 17));
-    for (int t = iw; ok; t += kRowIssuers) {
+    for (int t = iw; ok && iw < p.issuers; t += p.issuers) {
       const int tile = blockIdx.x + t * (int)gridDim.x;
       if (tile >= tiles) break;
       const int a_g = t * p.cchunks, b_g = a_g * b_per_cc;
@@ -338,6 +339,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     int t = 0;
     const bool vec_ok = (p.ldo % 4 == 0) &&
                         (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias) | reinterpret_cast<uintptr_t>(p.addend)) & 15u) == 0);
+    const bool wide_ok = vec_ok && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 31u) == 0);  // 32-byte stores
     // statistics variant: narrow tiles keep per-lane sums (cheap per tile), wide tiles merge per tile
     constexpr bool LANE_SUMS = STATS && BN == 64;
     WarpColStats<(STATS && !LANE_SUMS) ? BN / 32 : 1> stats;
@@ -375,6 +377,54 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       tc_fence_after();
+      if constexpr (BN == 64 && MT == 1) {
+        // Narrow tiles, whole column tile, 32-byte aligned rows: every lane stores runs of eight floats (whole
+        // sectors).  With statistics the accumulator is read out whole and handed back to the issuing warps
+        // before the arithmetic; without, reading and storing half by half measured faster.
+        if (wide_ok && n0 + 64 <= p.N && !p.addend) {
+          const uint32_t t_addr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(buf * BN);
+          float* orow = p.out + ooff[0] + n0;
+          auto put = [&](const uint32_t (&r)[32], int c0) {
+            if (!valid[0]) return;
+#pragma unroll
+            for (int j = 0; j < 32; j += 8) {
+              float o[8];
+#pragma unroll
+              for (int k = 0; k < 8; ++k) {
+                o[k] = __uint_as_float(r[j + k]) + (p.bias ? __ldg(p.bias + n0 + c0 + j + k) : 0.f);
+                if (p.relu) o[k] = fmaxf(o[k], 0.f);
+              }
+              st_global_v8(orow + c0 + j, o[0], o[1], o[2], o[3], o[4], o[5], o[6], o[7]);
+            }
+          };
+          if constexpr (STATS) {
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(t_addr, r0);
+            tmem_ld_32x32(t_addr + 32, r1);
+            tmem_ld_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+            put(r0, 0);
+            put(r1, 32);
+            // per-lane sums of the raw accumulator (the bias is the pivot)
+            if (valid[0]) { sums.add_chunk(0, r0); sums.add_chunk(1, r1); }
+            sums.cnt += valid[0] ? 1.f : 0.f;
+          } else {
+#pragma unroll
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+              uint32_t r[32];
+              tmem_ld_32x32(t_addr + c0, r);
+              tmem_ld_wait();
+              put(r, c0);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&bar_tempty[buf]));
+          }
+          continue;
+        }
+      }
       if constexpr (STATS) {
         // forward convolution feeding a BatchNorm layer (no addend, N % 32 == 0, aligned: checked on the
         // host): store the rows and fold them into the per-channel statistics
@@ -394,7 +444,8 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
               for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + col0 + j) : 0.f);
               if (valid[m]) {
 #pragma unroll
-                for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + col0 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+                for (int j = 0; j < 32; j += 8)
+                  st_row8(orow + col0 + j, make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]), make_float4(o[j + 4], o[j + 5], o[j + 6], o[j + 7]), wide_ok);
               }
               if constexpr (LANE_SUMS) {
                 if (valid[m]) sums.add_chunk(c0 / 32, r);
@@ -423,18 +474,23 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           if (valid[m] && col0 < p.N) {
             if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 o = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (p.bias) {
-                  const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
+              for (int j = 0; j < 32; j += 8) {
+                float4 o[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int jj = j + 4 * h;
+                  o[h] = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
+                  if (p.bias) {
+                    const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + jj);
+                    o[h].x += b.x; o[h].y += b.y; o[h].z += b.z; o[h].w += b.w;
+                  }
+                  if (arow) {
+                    const float4 b = prefetched ? pre[kPre > 1 ? (c0 + jj) / 4 : 0] : *reinterpret_cast<const float4*>(arow + col0 + jj);
+                    o[h].x += b.x; o[h].y += b.y; o[h].z += b.z; o[h].w += b.w;
+                  }
+                  if (p.relu) { o[h].x = fmaxf(o[h].x, 0.f); o[h].y = fmaxf(o[h].y, 0.f); o[h].z = fmaxf(o[h].z, 0.f); o[h].w = fmaxf(o[h].w, 0.f); }
                 }
-                if (arow) {
-                  const float4 b = prefetched ? pre[kPre > 1 ? (c0 + j) / 4 : 0] : *reinterpret_cast<const float4*>(arow + col0 + j);
-                  o.x += b.x; o.y += b.y; o.z += b.z; o.w += b.w;
-                }
-                if (p.relu) { o.x = fmaxf(o.x, 0.f); o.y = fmaxf(o.y, 0.f); o.z = fmaxf(o.z, 0.f); o.w = fmaxf(o.w, 0.f); }
-                *reinterpret_cast<float4*>(orow + col0 + j) = o;
+                st_row8(orow + col0 + j, o[0], o[1], wide_ok);
               }
             } else {
 #pragma unroll
@@ -589,6 +645,7 @@ int run_row_conv(const RowConvPlan& plan, int bn, int n, int h, int w, int kc, i
   p.m_tiles = (int)((p.Q + 127) / 128); p.n_tiles = (nout + bn - 1) / bn;
   p.a_stage_bytes = plan.a_stage_bytes; p.b_stages = plan.b_stages; p.tps = plan.tps; p.resident = plan.resident;
   p.out = out; p.ldo = nout; p.bias = bias; p.addend = addend; p.relu = relu;
+  p.issuers = getenv("MTB_ROWCONV_ONE_ISSUER") ? 1 : kRowIssuers;
   p.stats = stats;
   if (b_tap_x) for (int j = 0; j < kh * kw; ++j) p.b_tap_x[j] = b_tap_x[j];
   return launch_row_conv_bn<BMODE>(bn, plan.mt, mapA, mapB, p, plan.smem_bytes, st);
@@ -780,6 +837,7 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
       const long long Kw = (long long)p.KH * p.KW * p.Cin;
       float* part = p.partial + (long long)split * Kw * p.Cout;
       const bool vec_ok = (p.Cout % 4 == 0) && ((reinterpret_cast<uintptr_t>(p.partial) & 15u) == 0);
+      const bool wide_ok = (p.Cout % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.partial) & 31u) == 0);
       int a = 0;
       for (int c = 0; c < ncc; ++c)
         for (int kh = 0; kh < p.KH; ++kh)
@@ -796,9 +854,9 @@ tc_wgrad_rows_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_cons
               if (valid && n0 + c0 < p.Cout) {
                 if (vec_ok && n0 + c0 + 32 <= p.Cout) {
 #pragma unroll
-                  for (int j = 0; j < 32; j += 4)
-                    *reinterpret_cast<float4*>(orow + c0 + j) =
-                        make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
+                  for (int j = 0; j < 32; j += 8)
+                    st_row8(orow + c0 + j, make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                            make_float4(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]), __uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])), wide_ok);
                 } else {
 #pragma unroll
                   for (int j = 0; j < 32; ++j)

@@ -304,6 +304,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
     const int quarter = warp & 3;
     int t = 0;
     const bool vec_ok = (p.ldo % 4 == 0) && (((reinterpret_cast<uintptr_t>(p.out) | reinterpret_cast<uintptr_t>(p.bias)) & 15u) == 0);
+    const bool wide_ok = vec_ok && (p.ldo % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.out) & 31u) == 0);  // 32-byte stores
     // statistics variant: narrow tiles keep per-lane sums (cheap per tile), wide tiles merge per tile
     constexpr bool LANE_SUMS = STATS && BN == 64;
     WarpColStats<(STATS && !LANE_SUMS) ? BN / 32 : 1> stats;
@@ -341,7 +342,8 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
             for (int j = 0; j < 32; ++j) o[j] = __uint_as_float(r[j]) + (p.bias ? __ldg(p.bias + col0 + j) : 0.f);
             if (valid) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(orow + col0 + j) = make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]);
+              for (int j = 0; j < 32; j += 8)
+                st_row8(orow + col0 + j, make_float4(o[j], o[j + 1], o[j + 2], o[j + 3]), make_float4(o[j + 4], o[j + 5], o[j + 6], o[j + 7]), wide_ok);
             }
             if constexpr (LANE_SUMS) {
               if (valid) sums.add_chunk(c0 / 32, r);
@@ -353,14 +355,19 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
           if (valid && col0 < p.N) {
             if (vec_ok && col0 + 32 <= p.N) {
 #pragma unroll
-              for (int j = 0; j < 32; j += 4) {
-                float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-                if (p.bias) {
-                  const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + j);
-                  v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w;
+              for (int j = 0; j < 32; j += 8) {
+                float4 v[2];
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                  const int jj = j + 4 * h;
+                  v[h] = make_float4(__uint_as_float(r[jj]), __uint_as_float(r[jj + 1]), __uint_as_float(r[jj + 2]), __uint_as_float(r[jj + 3]));
+                  if (p.bias) {
+                    const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + jj);
+                    v[h].x += b.x; v[h].y += b.y; v[h].z += b.z; v[h].w += b.w;
+                  }
+                  if (p.relu) { v[h].x = fmaxf(v[h].x, 0.f); v[h].y = fmaxf(v[h].y, 0.f); v[h].z = fmaxf(v[h].z, 0.f); v[h].w = fmaxf(v[h].w, 0.f); }
                 }
-                if (p.relu) { v.x = fmaxf(v.x, 0.f); v.y = fmaxf(v.y, 0.f); v.z = fmaxf(v.z, 0.f); v.w = fmaxf(v.w, 0.f); }
-                *reinterpret_cast<float4*>(orow + col0 + j) = v;
+                st_row8(orow + col0 + j, v[0], v[1], wide_ok);
               }
             } else {
 #pragma unroll
@@ -992,6 +999,7 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
   } else {
     const int quarter = warp & 3;
     int t = 0;
+    const bool wide_ok = (p.Cout % 8 == 0) && ((reinterpret_cast<uintptr_t>(p.partial) & 31u) == 0);  // 32-byte stores
     for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++t) {
       const int split = unit % p.splits, tile = unit / p.splits;
       const int m_tile = tile / p.n_tiles, n0 = (tile % p.n_tiles) * BN;
@@ -1015,10 +1023,11 @@ tc_wgrad_kernel(const __grid_constant__ CUtensorMap mapX, const __grid_constant_
         if (row < p.Kw && col0 < p.Cout) {
           if (col0 + 32 <= p.Cout) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4) {
+            for (int j = 0; j < 32; j += 8) {
               float4 v = make_float4(__uint_as_float(r[j]), __uint_as_float(r[j + 1]), __uint_as_float(r[j + 2]), __uint_as_float(r[j + 3]));
-              if (empty_unit) v = make_float4(0.f, 0.f, 0.f, 0.f);
-              *reinterpret_cast<float4*>(orow + col0 + j) = v;
+              float4 u = make_float4(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5]), __uint_as_float(r[j + 6]), __uint_as_float(r[j + 7]));
+              if (empty_unit) v = u = make_float4(0.f, 0.f, 0.f, 0.f);
+              st_row8(orow + col0 + j, v, u, wide_ok);
             }
           } else {
 #pragma unroll
