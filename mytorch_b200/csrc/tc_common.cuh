@@ -84,6 +84,24 @@ __device__ __forceinline__ void st_row8(float* p, float4 a, float4 b, bool wide)
   }
 }
 
+// Bounded wait for a shared-memory counter another warp of the CTA advances (kernels with two MMA-issuing
+// warps use it to order their parity waits on ring slots that both consume).
+__device__ __forceinline__ bool lap_wait(volatile int* seen, int lap, volatile int* abort_flag, int code) {
+  if (*seen >= lap) return true;
+  const long long start = clock64();
+  for (uint32_t it = 1;; ++it) {
+    if (*seen >= lap) return true;
+    if ((it & 63u) == 0u) {
+      if (*abort_flag) return false;
+      if (clock64() - start > kWaitCycles) {
+        *abort_flag = 1;
+        atomicCAS(&g_tc_status[0], 0, code);
+        return false;
+      }
+    }
+  }
+}
+
 // ---- TMA loads (global -> shared, completion on an mbarrier) ----
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"

@@ -59,25 +59,6 @@ constexpr int kRowThreads = 32 * (1 + kRowIssuers + 4);  // producer, issuers, f
 // MT = tiles of 128 positions per work item.  With streamed weights two tiles share every weight
 // stage (two accumulators), which halves the L2 -> shared-memory weight traffic per MMA; that traffic,
 // at ~47 B/cycle/SM, is what bounds the 128-channel layers.
-// A ring slot is consumed by whichever issuing warp owns the tile, and a parity wait cannot tell "lap L not
-// yet filled" from "lap L + 1 filled".  So the warp that has seen lap L of a slot filled publishes L + 1 in
-// shared memory, and nobody starts waiting for lap L + 1 before that (bounded like every other wait).
-__device__ __forceinline__ bool lap_wait(volatile int* seen, int lap, volatile int* abort_flag, int code) {
-  if (*seen >= lap) return true;
-  const long long start = clock64();
-  for (uint32_t it = 1;; ++it) {
-    if (*seen >= lap) return true;
-    if ((it & 63u) == 0u) {
-      if (*abort_flag) return false;
-      if (clock64() - start > kWaitCycles) {
-        *abort_flag = 1;
-        atomicCAS(&g_tc_status[0], 0, code);
-        return false;
-      }
-    }
-  }
-}
-
 template <int BN, int BMODE, int FK, int MT, bool STATS>
 __global__ void __launch_bounds__(kRowThreads, 1)
 tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const RowConvParams p) {
@@ -86,7 +67,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
   __shared__ uint64_t bar_afull[kRowAStages], bar_aempty[kRowAStages], bar_bfull[8], bar_bempty[8], bar_tfull[2], bar_tempty[2], bar_bres;
   __shared__ uint32_t tmem_slot;
   __shared__ int abort_flag;
-  __shared__ int seen_a[kRowAStages], seen_b[8];  // laps of each ring slot an issuing warp has seen filled
+  __shared__ int tiles_seen;  // tiles of this CTA whose every stage an issuing warp has seen filled
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -115,8 +96,7 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     }
     mbar_init(smem_u32(&bar_bres), 1);
     abort_flag = 0;
-    for (int s = 0; s < kRowAStages; ++s) seen_a[s] = 0;
-    for (int s = 0; s < 8; ++s) seen_b[s] = 0;
+    tiles_seen = 0;
     fence_barrier_init();
   }
   if (warp == 1) {
@@ -211,7 +191,10 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
     // between tiles (waiting for the accumulator and the next activation stage, position arithmetic, commits)
     // then runs while the other warp's MMAs keep the tensor pipe busy.  The two never accumulate into the same
     // buffer, so the interleaving of their MMAs in the pipe does not change any sum.  The rings are consumed in
-    // tile order, so a warp finds its place in them from the tile's ordinal alone.
+    // tile order, so a warp finds its place in them from the tile's ordinal alone.  A parity wait cannot tell
+    // "lap L not yet filled" from "lap L + 1 filled", and the previous lap of a slot may belong to the other
+    // warp's tile: so a warp publishes its tile's ordinal once it has seen the tile's last stage filled, and
+    // nobody starts waiting on the stages of tile t before tile t - 1 is published (bounded like every wait).
     const int iw = warp - 1;
     const int b_per_cc = p.resident ? 0 : (FK == 3 ? 3 : (taps + p.tps - 1) / p.tps);
     bool ok = true;
@@ -225,16 +208,16 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
       const int col = ((tile / p.n_tiles) * (128 * MT)) % p.Wp;
       const int buf = t & 1;
       const uint32_t use = (uint32_t)(t >> 1);
-      ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 13));
+      ok = __all_sync(0xffffffffu, lap_wait(&tiles_seen, t, abort_ptr, 18) &&
+                                       mbar_wait(smem_u32(&bar_tempty[buf]), (use & 1u) ^ 1u, abort_ptr, 13));
       if (!ok) break;
       tc_fence_after();
       const uint32_t d_tmem = tmem_base + buf * (MT * BN);
       constexpr uint32_t tile_step = 128u * 8u;  // the next tile's positions start 128 pixels (of 8 units) further
       for (int cc = 0; cc < p.cchunks && ok; ++cc) {
-        ok = __all_sync(0xffffffffu, lap_wait(&seen_a[as], alap, abort_ptr, 18) &&
-                                         mbar_wait(smem_u32(&bar_afull[as]), (uint32_t)alap & 1u, abort_ptr, 14));
+        ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_afull[as]), (uint32_t)alap & 1u, abort_ptr, 14));
         if (!ok) break;
-        *(volatile int*)&seen_a[as] = alap + 1;
+        if (p.resident && cc == p.cchunks - 1) *(volatile int*)&tiles_seen = t + 1;
         tc_fence_after();
         // position q0 of this tile sits PH rows and `col` pixels into the staged rows; tap
         // (kh, kw) reads (kh - PH) rows and (kw - PW) pixels away from it
@@ -273,10 +256,9 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           // streamed weights, 3x3 filter: one filter row (3 taps) per weight stage, straight-line issue
 #pragma unroll
           for (int kh = 0; kh < 3; ++kh) {
-            ok = __all_sync(0xffffffffu, lap_wait(&seen_b[bs], blap, abort_ptr, 19) &&
-                                             mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
             if (!ok) break;
-            *(volatile int*)&seen_b[bs] = blap + 1;
+            if (kh == 2 && cc == p.cchunks - 1) *(volatile int*)&tiles_seen = t + 1;
             tc_fence_after();
             const uint32_t b_row = b_lo0 + bs * (b_stage_bytes >> 4);
             if (elect_one()) {
@@ -299,10 +281,9 @@ tc_conv_rows_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_const
           int kh = 0, kw = 0;
           for (int tap0 = 0; tap0 < taps && ok; tap0 += p.tps) {
             const int cnt = taps - tap0 < p.tps ? taps - tap0 : p.tps;
-            ok = __all_sync(0xffffffffu, lap_wait(&seen_b[bs], blap, abort_ptr, 19) &&
-                                             mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
+            ok = __all_sync(0xffffffffu, mbar_wait(smem_u32(&bar_bfull[bs]), (uint32_t)blap & 1u, abort_ptr, 15));
             if (!ok) break;
-            *(volatile int*)&seen_b[bs] = blap + 1;
+            if (tap0 + p.tps >= taps && cc == p.cchunks - 1) *(volatile int*)&tiles_seen = t + 1;
             tc_fence_after();
             if (elect_one()) {
               uint32_t b_lo = b_lo0 + bs * (b_stage_bytes >> 4);
