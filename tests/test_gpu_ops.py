@@ -345,6 +345,53 @@ def test_sgd(g):
             assert rel_err(g.host(opt.state[p]["momentum_buffer"]), gd[f"sgd{i}_buf"]) < FP32_TOL
 
 
+def test_sgd_multi_tensor_over_ragged_sizes(g):
+    """One multi-tensor launch over tensors of very different sizes (a CTA per 4096 elements of one tensor):
+    sizes below, at and just past a chunk, an odd tail, and a second step that reads the momentum buffer."""
+    import mytorch_b200.nn as nn
+    from mytorch_b200.optim import SGD
+
+    rng = np.random.default_rng(21)
+    sizes = [1, 3, 64, 4095, 4096, 4097, 3 * 4096 + 5, 70001, 8]
+    kw = dict(lr=0.05, momentum=0.9, weight_decay=1e-3, nesterov=True)
+    host_p = [rng.standard_normal(n).astype(np.float32) for n in sizes]
+    host_b = [None] * len(sizes)
+    params = [nn.Parameter(g.dev(a.copy())) for a in host_p]
+    opt = SGD(params, **kw)
+    for step in range(2):
+        grads = [rng.standard_normal(n).astype(np.float32) for n in sizes]
+        for p, gr in zip(params, grads):
+            p.grad = g.dev(gr)
+        opt.step()
+        for i, gr in enumerate(grads):
+            host_p[i], host_b[i] = O.sgd_step(host_p[i], gr, host_b[i], step == 0, **kw)
+        for i, p in enumerate(params):
+            assert rel_err(g.host(p.detach()), host_p[i]) < FP32_TOL, (step, sizes[i])
+            assert rel_err(g.host(opt.state[p]["momentum_buffer"]), host_b[i]) < FP32_TOL, (step, sizes[i])
+
+
+def test_strided_data_gradient_side_by_side_equals_serial(g, monkeypatch):
+    """The residue classes of a strided data gradient run on separate lanes when each fills only part of the
+    GPU; the result is bit-identical to running them one after the other."""
+    rng = np.random.default_rng(8)
+    for (n, cin, cout, hw, k, pad) in [(16, 64, 128, 32, 3, 1), (8, 128, 256, 16, 3, 1), (16, 64, 128, 32, 1, 0)]:
+        x = rng.standard_normal((n, cin, hw, hw)).astype(np.float32)
+        wt = (rng.standard_normal((cout, cin, k, k)) / 16).astype(np.float32)
+        dy = rng.standard_normal((n, cout, hw // 2, hw // 2)).astype(np.float32)
+        results = []
+        for serial in (False, True):
+            if serial:
+                monkeypatch.setenv("MTB_DGRAD_SERIAL", "1")
+            else:
+                monkeypatch.delenv("MTB_DGRAD_SERIAL", raising=False)
+            dx, _, _ = g.op("conv2d_backward")(g.dev(dy), g.dev(x, True), g.dev(wt, True), None, (2, 2), (pad, pad))
+            results.append(g.host(dx))
+        monkeypatch.delenv("MTB_DGRAD_SERIAL", raising=False)
+        assert np.array_equal(results[0], results[1])
+        ref = O.conv2d_backward(dy, x, wt, False, (2, 2), (pad, pad))[0]
+        assert rel_err(results[0], ref) < TF32_TOL
+
+
 def test_errors_are_python_exceptions(g):
     import mytorch_b200 as mt
 
