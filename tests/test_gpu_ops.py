@@ -113,10 +113,12 @@ def test_conv_two_tiles_per_weight_stage(g, cfg, monkeypatch):
     _conv_check(g, x, wt, b, dy, s, p)
 
 
-@pytest.mark.parametrize("cfg", [(8, 64, 32, 32, 64, 3, 1, 1), (8, 64, 32, 32, 128, 3, 2, 1), (2, 20, 9, 11, 24, 3, 1, 1), (8, 3, 32, 32, 64, 3, 1, 1)])
+@pytest.mark.parametrize("cfg", [(8, 64, 32, 32, 64, 3, 1, 1), (8, 64, 32, 32, 128, 3, 2, 1), (2, 20, 9, 11, 24, 3, 1, 1), (8, 3, 32, 32, 64, 3, 1, 1),
+                                 (8, 64, 32, 32, 128, 1, 2, 0), (16, 256, 8, 8, 512, 3, 2, 1), (64, 128, 16, 16, 256, 3, 2, 1)])
 def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
     """dx returned with ``accumulate_dx`` equals dgrad + that tensor bit for bit, on the row-staged
-    path (sum in the epilogue), the im2col path, the CUDA-core path and the channel-padded stem."""
+    path (sum in the epilogue), the im2col path (stride 2, also with residue classes side by side and classes
+    without taps: sum afterwards), the CUDA-core path and the channel-padded stem."""
     n, ci, h, w, co, k, s, p = cfg
     rng = np.random.default_rng(11)
     x = rng.standard_normal((n, ci, h, w)).astype(np.float32)
