@@ -104,10 +104,15 @@ int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, i
                          const float* wt, float* dx, void* workspace, long long workspace_bytes, void* stream);
 /* dx = data gradient + addend (addend: same shape as dx, not aliasing it): gradient accumulation for
  * a tensor with a second consumer, fused into the convolution's epilogue where the kernel allows.
+ * Where mtb_conv2d_dgrad_accumulates_in_place answers 1 (strided convolutions whose filter is smaller than
+ * the stride, e.g. the 1x1 / stride-2 shortcut of a residual stage), addend == dx is allowed and means
+ * dx += data gradient: only the pixels a filter tap reaches are touched.
  * No counterpart in the reference, whose tape adds the two gradients with a separate `add`
  * (mytorch/autograd.py:160-170). */
 int mtb_conv2d_dgrad_add_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                              const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream);
+int mtb_conv2d_dgrad_accumulates_in_place(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout,
+                                          const float* dy, const float* wt, const float* dx);
 /* Introspection, host code only (works without a GPU): which kernel family forward / dgrad / wgrad
  * would take for this shape and how the row-staged kernels lay out shared and tensor memory.
  * out: 25 ints, see the definition in csrc/tc_kernels.cu.  No counterpart in the reference. */

@@ -73,6 +73,7 @@ _SIGNATURES = {
     "mtb_batch_norm2d_forward_prestats_f32": ([_I, _I, _I, _I, _P, _P, _P, _D, _D, _P, _P, _P, _P, _P, _I, _P, _I, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_conv2d_dgrad_add_f32": (_CONV + [_P, _P, _P, _P, _P, _L, _P], _I),
+    "mtb_conv2d_dgrad_accumulates_in_place": (_CONV + [_P, _P, _P], _I),
     "mtb_conv2d_wgrad_f32": (_CONV + [_P, _P, _P, _P, _L, _P], _I),
     "mtb_gemm_f32": ([_I, _I, _I, _P, _I, _P, _I, _P, _I, _P, _P], _I),
     "mtb_tc_status": ([_P], _I),
@@ -145,7 +146,7 @@ class NativeLibrary:
             fn.restype = restype
             if restype is _P:
                 wrapped = self._pointer(name, fn)
-            elif restype is _I and name not in ("mtb_version", "mtb_conv2d_stats_max_rows"):
+            elif restype is _I and name not in ("mtb_version", "mtb_conv2d_stats_max_rows", "mtb_conv2d_dgrad_accumulates_in_place"):
                 wrapped = self._checked(name, fn, name not in _NOT_LAUNCHES)
             else:
                 wrapped = fn

@@ -239,10 +239,17 @@ def cuda_conv2d_backward(output_grad, input, weight, bias, stride, padding, accu
     ws, ws_bytes = env.workspace(env.lib.conv2d_workspace_bytes(*a))
     dx = dw = db = None
     if want_dx:
-        dx = _new(x.shape, x)
-        if accumulate_dx is not None and not padded:
+        if accumulate_dx is not None and not padded and env.lib.conv2d_dgrad_accumulates_in_place(
+                *a, _ptr(output_grad), _ptr(wt), _ptr(accumulate_dx)):
+            # a filter smaller than its stride (the 1x1 / stride-2 shortcut) reaches only some pixels: it adds
+            # to those in the gradient the input already holds, which is then the returned tensor
+            dx = accumulate_dx
+            env.lib.conv2d_dgrad_add_f32(*a, _ptr(output_grad), _ptr(wt), _ptr(dx), _ptr(dx), ws, ws_bytes, st)
+        elif accumulate_dx is not None and not padded:
+            dx = _new(x.shape, x)
             env.lib.conv2d_dgrad_add_f32(*a, _ptr(output_grad), _ptr(wt), _ptr(accumulate_dx), _ptr(dx), ws, ws_bytes, st)
         else:
+            dx = _new(x.shape, x)
             env.lib.conv2d_dgrad_f32(*a, _ptr(output_grad), _ptr(wt), _ptr(dx), ws, ws_bytes, st)
             if padded:
                 dx = _take_channels(env, dx, cin, dx)

@@ -49,15 +49,28 @@ MTB_API int mtb_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, i
 // dx = dgrad(dy, wt) + addend: the data gradient added to a gradient the same tensor already received
 // from another consumer (residual connections).  On the row-staged tensor-core path the sum happens
 // in the epilogue, which saves one pass over dx and one launch; elsewhere it is dgrad followed by an
-// add.  addend has the shape of dx and must not alias it.
+// add.  addend has the shape of dx and must not alias it, except where
+// mtb_conv2d_dgrad_accumulates_in_place answers 1: there addend == dx means dx += data gradient.
 MTB_API int mtb_conv2d_dgrad_add_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                                      const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream) {
-  MTB_REQUIRE(addend && addend != dx, "conv2d_dgrad_add: addend must be given and must not alias dx");
+  MTB_REQUIRE(addend, "conv2d_dgrad_add: addend must be given");
+  if (addend == dx) {  // accumulate in place: only where mtb_conv2d_dgrad_accumulates_in_place says so
+    MTB_REQUIRE(mtb_tc_conv2d_dgrad_in_place(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx),
+                "conv2d_dgrad_add: this shape cannot accumulate in place (addend must not alias dx)");
+    return mtb_tc_conv2d_dgrad_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, addend, dx, workspace, workspace_bytes, stream);
+  }
   if (mtb_tc_conv2d_dgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx))
     return mtb_tc_conv2d_dgrad_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, addend, dx, workspace, workspace_bytes, stream);
   int rc = mtb_conv2d_dgrad_simt_f32(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx, stream);
   if (rc) return rc;
   return mtb_add_f32(dx, addend, dx, (long long)n * h * w * cin, 1.0f, stream);
+}
+
+// 1 when mtb_conv2d_dgrad_add_f32 may be called with addend == dx for this convolution (dx += data gradient,
+// nothing else touched) and that is its cheaper form; 0 otherwise.  Host code only.
+MTB_API int mtb_conv2d_dgrad_accumulates_in_place(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout,
+                                                  const float* dy, const float* wt, const float* dx) {
+  return mtb_tc_conv2d_dgrad_in_place(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx) ? 1 : 0;
 }
 
 MTB_API int mtb_conv2d_wgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* x,

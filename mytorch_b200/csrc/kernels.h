@@ -22,6 +22,8 @@ int mtb_tc_conv2d_forward_f32(int n, int cin, int h, int w, int kh, int kw, int 
                               float* stats = nullptr, int* stats_rows = nullptr);
 bool mtb_tc_conv2d_dgrad_supported(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                                    const float* wt, const float* dx);
+bool mtb_tc_conv2d_dgrad_in_place(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                                  const float* wt, const float* dx);
 int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
                             const float* wt, const float* addend, float* dx, void* workspace, long long workspace_bytes, void* stream);
 MTB_API int mtb_add_f32(const float* x, const float* y, float* z, long long n, float alpha, void* stream);

@@ -108,6 +108,9 @@ struct GemmParams {
   float* out;
   long long ldo;
   const float* bias;
+  // optional: out += result instead of out = result (the rows of `out` already hold a value this launch adds
+  // to; a thread reads the very elements it then writes, so accumulating in place is safe)
+  int accumulate;
   int relu;
   // geometry of the im2col'ed tensor (A operand of a convolution)
   int OW, OH, SW, SH, PW, PH, KW, KH, cchunks;
@@ -365,6 +368,10 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                     const float4 b = *reinterpret_cast<const float4*>(p.bias + col0 + jj);
                     v[h].x += b.x; v[h].y += b.y; v[h].z += b.z; v[h].w += b.w;
                   }
+                  if (p.accumulate) {
+                    const float4 b = *reinterpret_cast<const float4*>(orow + col0 + jj);
+                    v[h].x += b.x; v[h].y += b.y; v[h].z += b.z; v[h].w += b.w;
+                  }
                   if (p.relu) { v[h].x = fmaxf(v[h].x, 0.f); v[h].y = fmaxf(v[h].y, 0.f); v[h].z = fmaxf(v[h].z, 0.f); v[h].w = fmaxf(v[h].w, 0.f); }
                 }
                 st_row8(orow + col0 + j, v[0], v[1], wide_ok);
@@ -375,6 +382,7 @@ tc_gemm_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__
                 if (col0 + j < p.N) {
                   float v = __uint_as_float(r[j]);
                   if (p.bias) v += p.bias[col0 + j];
+                  if (p.accumulate) v += orow[col0 + j];
                   if (p.relu) v = fmaxf(v, 0.f);
                   orow[col0 + j] = v;
                 }
@@ -787,7 +795,10 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
       Axis ah = axis(a, h, oh, kh, sh, ph), aw = axis(b, w, ow, kw, sw, pw);
       if (ah.count > 0 && aw.count > 0 && (ah.taps == 0 || aw.taps == 0)) need_zero = true;
     }
-  if (need_zero) MTB_CUDA(cudaMemsetAsync(dx, 0, (size_t)n * h * w * cin * 4, st));
+  // addend == dx: dx already holds the gradient to add to; every class adds its own pixels in its epilogue
+  // and the pixels of classes without taps stay as they are.
+  const bool in_place = addend != nullptr && addend == dx;
+  if (need_zero && !in_place) MTB_CUDA(cudaMemsetAsync(dx, 0, (size_t)n * h * w * cin * 4, st));
   // The classes write disjoint pixels.  When one class fills only part of the GPU they run side by side on
   // separate lanes (then without split reductions, whose tickets and partials one launch at a time owns).
   int live = 0;
@@ -819,6 +830,7 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
       p.splits = gp.splits; p.kb_per_split = gp.kb_per_split; p.partial = (float*)workspace;
       p.m_tiles = (int)((M + 127) / 128); p.n_tiles = (cin + bn - 1) / bn;
       p.out = dx; p.ldo = cin; p.bias = nullptr; p.relu = 0;
+      p.accumulate = in_place ? 1 : 0;
       p.OW = aw.count; p.OH = ah.count; p.SW = 1; p.SH = 1; p.PW = -aw.lower; p.PH = -ah.lower; p.KW = aw.taps; p.KH = ah.taps;
       p.cchunks = cout / 32;
       p.b_per_tap = 1;
@@ -834,8 +846,18 @@ int mtb_tc_conv2d_dgrad_f32(int n, int cin, int h, int w, int kh, int kw, int sh
   }
   rc = mtb_join_lanes(st, lanes);
   if (rc) return rc;
-  if (addend) return mtb_add_f32(dx, addend, dx, (long long)n * h * w * cin, 1.0f, st);
+  if (addend && !in_place) return mtb_add_f32(dx, addend, dx, (long long)n * h * w * cin, 1.0f, st);
   return MTB_OK;
+}
+
+// True when mtb_tc_conv2d_dgrad_f32 with addend == dx (accumulate in place) is available AND is the cheaper
+// form: strided convolutions some of whose residue classes have no taps (1x1 with stride 2), where the
+// out-of-place form costs a memset, a scattered write and a pass that adds the two tensors.
+bool mtb_tc_conv2d_dgrad_in_place(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout, const float* dy,
+                                  const float* wt, const float* dx) {
+  if (!mtb_tc_conv2d_dgrad_supported(n, cin, h, w, kh, kw, sh, sw, ph, pw, cout, dy, wt, dx)) return false;
+  if (sh * sw == 1 || getenv("MTB_DGRAD_OUT_OF_PLACE")) return false;
+  return kh < sh || kw < sw;  // a residue class a >= kh (b >= kw) sees no tap
 }
 
 // ------------------------------------------------------------------------------ weight gradient

@@ -53,10 +53,13 @@ class BasicBlock(nn.Module):
             _feed_batch_norm(self.conv1, self.conv2, *([self.downsample._modules["0"]] if self.downsample is not None else []))
 
     def forward(self, x):
+        # The projection shortcut is computed first: backward then meets it last, after conv1 has written a
+        # gradient for every pixel of x, and the 1x1 / stride-2 convolution adds its own in place to the
+        # pixels it reaches (instead of a zero-filled tensor that has to be added afterwards).
+        shortcut = x if self.downsample is None else self.downsample(x)
         y = self.bn1(self.conv1(x))
         if not self.fused:
             y = self.relu(y)
-        shortcut = x if self.downsample is None else self.downsample(x)
         if self.fused:
             return self.bn2(self.conv2(y), shortcut)
         return self.relu(self.bn2(self.conv2(y)) + shortcut)

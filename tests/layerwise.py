@@ -89,6 +89,8 @@ class LayerwiseChecker:
     def _backward(self, name, func):
         def wrapped(*args, **kwargs):
             kwargs.pop("defer_weight_gradient", None)  # every gradient is inspected right after its operator returns
+            # read before the call: an operator may add to this tensor in place and return it
+            earlier = _h(kwargs["accumulate_dx"]) if kwargs.get("accumulate_dx") is not None else None
             grads = func(*args, **kwargs)
             g = [_h(t) if t is not None and hasattr(t, "shape") else None for t in grads]
             if name == "conv2d":
@@ -96,8 +98,9 @@ class LayerwiseChecker:
                 rdx, rdw, rdb = O.conv2d_backward(_h(dy), _h(x.detach()), _h(w.detach()), b is not None, s, p)
                 tdx, tdw, _ = O.conv2d_backward(O.round_tf32(_h(dy)), O.round_tf32(_h(x.detach())), O.round_tf32(_h(w.detach())), False, s, p)
                 if g[0] is not None:
-                    acc = kwargs.get("accumulate_dx")  # the returned dx then includes this earlier gradient
-                    self._note("bwd", name + ".dx", g[0], rdx if acc is None else rdx + _h(acc), TF32_TOL, tdx if acc is None else tdx + _h(acc))
+                    # with accumulate_dx the returned dx includes that earlier gradient
+                    self._note("bwd", name + ".dx", g[0], rdx if earlier is None else rdx + earlier, TF32_TOL,
+                               tdx if earlier is None else tdx + earlier)
                 self._note("bwd", name + ".dw", g[1], rdw, TF32_TOL, tdw)
                 if b is not None:
                     self._note("bwd", name + ".db", g[2], rdb, FP32_TOL * 5)

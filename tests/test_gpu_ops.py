@@ -130,7 +130,10 @@ def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
     dx, _, _ = g.op("conv2d_backward")(dyt, xt, wtt, None, (s, s), (p, p))
     both, _, _ = g.op("conv2d_backward")(dyt, xt, wtt, None, (s, s), (p, p), accumulate_dx=pt)
     assert np.array_equal(g.host(both), g.host(dx) + prev)
-    assert np.array_equal(g.host(pt), prev)
+    if k < s:  # a filter smaller than its stride accumulates in place: the tensor handed in is the one returned
+        assert both is pt
+    else:
+        assert np.array_equal(g.host(pt), prev)
 
 
 @pytest.mark.parametrize("shape", [(8, 64, 16, 16), (8, 256, 8, 8), (16, 512, 4, 4)])
