@@ -230,6 +230,25 @@ def test_row_staged_kernels_never_plan_to_leave_their_memory():
         assert list(out[0:3]) == want, (cfg, list(out))
 
 
+def test_in_place_data_gradient_is_offered_only_where_the_filter_misses_pixels():
+    """Host-side query: a strided convolution whose filter is smaller than the stride (the 1x1 / stride-2 shortcut)
+    may add its data gradient in place; every other shape keeps the out-of-place form."""
+    import ctypes
+
+    from mytorch_b200.backends.cuda.env import LIBRARY_PATH
+
+    lib = ctypes.CDLL(LIBRARY_PATH)
+    fn = lib.mtb_conv2d_dgrad_accumulates_in_place
+    fn.argtypes = [ctypes.c_int] * 11 + [ctypes.c_void_p] * 3
+    fn.restype = ctypes.c_int
+    aligned = (ctypes.c_void_p(1 << 20),) * 3  # never dereferenced: the query looks at alignment only
+    assert fn(64, 64, 32, 32, 1, 1, 2, 2, 0, 0, 128, *aligned) == 1
+    assert fn(64, 64, 32, 32, 3, 3, 2, 2, 1, 1, 128, *aligned) == 0  # every residue class has a tap
+    assert fn(64, 64, 32, 32, 3, 3, 1, 1, 1, 1, 64, *aligned) == 0   # stride 1: summed in the epilogue, out of place
+    assert fn(64, 64, 32, 32, 1, 1, 2, 2, 0, 0, 128, ctypes.c_void_p((1 << 20) + 4), *aligned[:2]) == 0  # unaligned
+    assert fn(1, 3, 8, 8, 1, 1, 2, 2, 0, 0, 8, *aligned) == 0  # shapes the tensor-core family does not take
+
+
 def test_shard_bounds_cover_batch():
     from mytorch_b200.parallel import shard_bounds
 
