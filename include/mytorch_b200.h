@@ -80,7 +80,7 @@ int mtb_graph_launch(void* graph_exec, void* stream);
 int mtb_graph_destroy(void* graph_exec);
 
 /* ---- convolution (replaces ConvForwardImplicitGEMM_float32 / ConvBackwardImplicitGEMM_float32,
- *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-484, called from
+ *      mytorch/native/cuda/conv.cu/source.cu:419-443 and :445-483, called from
  *      mytorch/backends/cuda/ops/conv.py:9-90) ---- */
 long long mtb_conv2d_workspace_bytes(int n, int cin, int h, int w, int kh, int kw, int sh, int sw, int ph, int pw, int cout);
 /* y[N,OH,OW,Cout] = conv(x[N,H,W,Cin], wt[Cout,KH,KW,Cin]) + bias (bias may be NULL); relu != 0 clamps at 0.
