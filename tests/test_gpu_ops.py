@@ -136,11 +136,12 @@ def test_conv_backward_accumulates_into_existing_gradient(g, cfg):
         assert np.array_equal(g.host(pt), prev)
 
 
-@pytest.mark.parametrize("shape", [(8, 64, 16, 16), (8, 256, 8, 8), (16, 512, 4, 4)])
+@pytest.mark.parametrize("shape", [(8, 64, 16, 16), (8, 256, 8, 8), (16, 512, 4, 4), (96, 64, 32, 32), (128, 128, 16, 16)])
 def test_conv_is_deterministic(g, shape):
     """Bitwise-equal results on repeated runs, also for the layers whose forward pass and data gradient
-    split their reduction across CTAs (few output tiles: 8x8 and 4x4 images) and whose BatchNorm
-    statistics come from the convolution's epilogue."""
+    split their reduction across CTAs (few output tiles: 8x8 and 4x4 images), whose BatchNorm
+    statistics come from the convolution's epilogue, and whose CTAs run several tiles issued by two
+    warps in turn (the last two shapes: weights resident / streamed with two tiles per weight stage)."""
     n, c, h, w = shape
     rng = np.random.default_rng(5)
     x = rng.standard_normal((n, c, h, w)).astype(np.float32)
