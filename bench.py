@@ -391,14 +391,15 @@ def profile_leg(env, name, iters=3):
     profiled with ncu for the summaries under profiles/ (kept small so that a full-counter capture ends
     by itself).  conv64: 64->64 3x3 on 512x32x32 forward, forward with BatchNorm statistics, dgrad,
     wgrad; wgrad256: weight gradient of 256->256 3x3 on 512x8x8 (im2col kernel); pool: 2x2/2 max-pool
-    forward and backward on 256x128x56x56; bn64: BatchNorm forward / backward on 512x64x32x32."""
+    forward and backward on 256x128x56x56; bn64: BatchNorm forward / backward on 512x64x32x32; bn64add: the
+    same shape through the BatchNorm + shortcut add + ReLU operator of a residual block's tail."""
     import mytorch_b200 as mt
     from mytorch_b200.backends.backend_dispatcher import BackendDispatcher
 
     op = lambda n: BackendDispatcher.instance().dispatch("cuda", n)
     rng = np.random.default_rng(2)
     dev = lambda a, grad=False: mt.tensor(a.astype(np.float32), device="cuda", requires_grad=grad)
-    if name in ("conv64", "bn64"):
+    if name in ("conv64", "bn64", "bn64add"):
         x, dy = dev(rng.standard_normal((512, 64, 32, 32)), True), dev(rng.standard_normal((512, 64, 32, 32)))
         if name == "conv64":
             w = dev(rng.standard_normal((64, 64, 3, 3)) / 24, True)
@@ -406,11 +407,17 @@ def profile_leg(env, name, iters=3):
                 op("conv2d")(x, w, None, (1, 1), (1, 1))
                 op("conv2d")(x, w, None, (1, 1), (1, 1), bn_stats=True)
                 op("conv2d_backward")(dy, x, w, None, (1, 1), (1, 1))
-        else:
+        elif name == "bn64":
             g, b = dev(np.ones(64), True), dev(np.zeros(64), True)
             for _ in range(iters):
                 y, m, v = op("batch_norm2d")(x, g, b, 1e-5, True, 0.1, None, None)
                 op("batch_norm2d_backward")(dy, m, v, x, g, b, 1e-5)
+        else:
+            g, b = dev(np.ones(64), True), dev(np.zeros(64), True)
+            res = dev(rng.standard_normal((512, 64, 32, 32)), True)
+            for _ in range(iters):
+                y, m, v = op("batch_norm2d_add_relu")(x, res, g, b, 1e-5, True, 0.1, None, None)
+                op("batch_norm2d_add_relu_backward")(dy, m, v, x, res, g, b, 1e-5)
     elif name == "wgrad256":
         x, dy = dev(rng.standard_normal((512, 256, 8, 8))), dev(rng.standard_normal((512, 256, 8, 8)))
         w = dev(rng.standard_normal((256, 256, 3, 3)) / 48, True)
@@ -645,7 +652,7 @@ def main():
                     help="gradient all-reduce buckets (N>1): 1 = one all-reduce after backward, more = start each "
                          "bucket on a side stream as soon as backward has finished its gradients")
     ap.add_argument("--skip-legs", action="store_true", help="skip the single-kernel roofline and CPU-baseline legs")
-    ap.add_argument("--leg", default=None, choices=["conv64", "wgrad256", "pool", "bn64"],
+    ap.add_argument("--leg", default=None, choices=["conv64", "wgrad256", "pool", "bn64", "bn64add"],
                     help="run one operator at a benchmark shape for a few launches and exit (the small command profiled with ncu)")
     ap.add_argument("--only-legs", action="store_true",
                     help="run only the single-kernel legs (conv fwd/dgrad/wgrad, BatchNorm, ReLU) and print their JSON; "
